@@ -1,0 +1,138 @@
+/*
+ * rzlinear_b200 - C ABI of the B200 (sm_100a) RzLinear ROBE-Z compressed-matmul kernels.
+ *
+ * The library replaces the kernel launchers of the reference's python/rz_linear package
+ * (apd10/RzLinear).  Paths cited below are relative to that repository.
+ *
+ * Conventions
+ *   - Every pointer is a plain device pointer (host pointer where the name says "host");
+ *     the caller owns every buffer, the library allocates nothing the caller sees.
+ *   - `stream` is a cudaStream_t passed as void*; all launches are asynchronous on it.
+ *   - Matrices are contiguous row-major: X[M,K], Y[M,N], dY[M,N], dX[M,K]; the hashed array and
+ *     its gradient are fp32 [H].
+ *   - Return value: RZ_OK (0) or a negative rz_status; rz_status_string() names it.
+ *   - Virtual weight: W[k,n] = hashed[ offset(k / BK, n / BN) + (k % BK) * BN + (n % BN) ].
+ */
+#ifndef RZLINEAR_B200_H
+#define RZLINEAR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum rz_status {
+    RZ_OK = 0,
+    RZ_ERR_NULL = -1,          /* a required pointer is NULL */
+    RZ_ERR_SHAPE = -2,         /* a dimension is <= 0 or too large */
+    RZ_ERR_HASH_RANGE = -3,    /* H <= BK*BN (the reference asserts H > BK*BN) */
+    RZ_ERR_DTYPE = -4,         /* unknown io_dtype / precision combination */
+    RZ_ERR_ALIGN = -5,         /* a pointer is not aligned as the kernels need (16 bytes) */
+    RZ_ERR_HASH_PARAM = -6,    /* R[0] (the prime) <= 0, a negative R, or unknown hash mode */
+    RZ_ERR_CUDA = -7,          /* a CUDA runtime/driver call failed (see rz_last_cuda_error) */
+    RZ_ERR_PIPELINE = -8,      /* a device-side bounded wait gave up (reported by rz_device_status) */
+    RZ_ERR_UNSUPPORTED = -9,   /* the requested path cannot run this problem */
+    RZ_ERR_TOO_LARGE = -10     /* size exceeds a fixed capacity of the entry point */
+};
+
+enum rz_hash_mode {
+    /* ((pk*R3 + pn*R2 + R1) mod R0) mod (H - BK*BN)
+       python/rz_linear/impl/RzLinearIdx.py:70-71, python/tests/test_rz_linear.py:26-27 */
+    RZ_HASH_SINGLE = 0,
+    /* ((((pk*R3+pn*R2+R1) mod R0)*R0 + ((pk*R7+pn*R5+R4) mod R0)) mod (H - BK*BN))
+       python/rz_linear/impl/RzLinearForward.py:316,349; RzLinearBackward.py:369,686,716 */
+    RZ_HASH_TWO_LEVEL = 1
+};
+
+enum rz_dtype { RZ_F32 = 0, RZ_BF16 = 1 };
+
+enum rz_precision {
+    RZ_PREC_FP32 = 0,  /* fp32 FMA arithmetic (reference: allow_tf32=False) */
+    RZ_PREC_TF32 = 1,  /* tf32 tensor cores, fp32 accumulate (reference: allow_tf32=True); io fp32 */
+    RZ_PREC_BF16 = 2   /* bf16 tensor cores, fp32 accumulate; io bf16, hashed array fp32 */
+};
+
+enum rz_flags {
+    RZ_FLAG_ACCUMULATE_DH = 1,  /* backward_weight adds into dH instead of zeroing it first */
+    RZ_FLAG_FORCE_SIMT = 2,     /* never take the tensor-core path */
+    RZ_FLAG_RELU = 4            /* forward: Y = max(0, X.W*alpha + bias) */
+};
+
+enum rz_op { RZ_OP_FORWARD = 0, RZ_OP_BACKWARD_INPUT = 1, RZ_OP_BACKWARD_WEIGHT = 2 };
+enum rz_path { RZ_PATH_SIMT = 0, RZ_PATH_TCGEN05 = 1 };
+
+typedef struct rz_problem {
+    int64_t M, K, N, H;   /* X[M,K], virtual W[K,N], hashed[H] */
+    int32_t BK, BN;       /* hash tile: part of the definition of the virtual matrix */
+    int32_t hash_mode;    /* enum rz_hash_mode */
+    int32_t io_dtype;     /* enum rz_dtype of X, Y, dY, dX */
+    int32_t precision;    /* enum rz_precision */
+    int32_t flags;        /* enum rz_flags, or-ed */
+    int64_t R[8];         /* random numbers, R[0] = the prime (python/rz_linear/RzLinear.py:68-74) */
+    float alpha;          /* init_factor (RzLinearForward.py:357, RzLinearBackward.py:371,727) */
+    int32_t reserved;
+} rz_problem;
+
+int rz_version(void);
+const char *rz_status_string(int status);
+/* Text of the last CUDA error seen by this thread's last failing call ("" if none). */
+const char *rz_last_cuda_error(void);
+
+/* Tile offsets on the host, out[cdiv(K,BK) * cdiv(N,BN)] row-major over (pk, pn).
+   Replaces the index arithmetic of RzLinearIdx.py:62-71 / RzLinearForward.py:316. */
+int rz_hash_indices_host(const rz_problem *pb, int64_t *out_host);
+
+/* The same offsets computed on the device by the routine the kernels use (device pointer out). */
+int rz_hash_indices_device(const rz_problem *pb, int64_t *out_dev, void *stream);
+
+/* Which kernel family would run `op` for this problem: RZ_PATH_SIMT or RZ_PATH_TCGEN05 (>= 0),
+   or a negative status if the problem is invalid. */
+int rz_plan(const rz_problem *pb, int op);
+
+/* Scratch ("shadow") memory the tensor-core forward / input-gradient kernels read instead of
+   the fp32 hashed array: element-shifted copies in the compute type so that every tile slice
+   starts on a 16-byte boundary of one copy.  rz_shadow_bytes() is 0 when the problem takes the
+   SIMT path.  The caller allocates `shadow` (256-byte aligned), and refreshes it whenever
+   `hashed` changes. */
+size_t rz_shadow_bytes(const rz_problem *pb);
+int rz_shadow_refresh(const rz_problem *pb, const float *hashed, void *shadow, void *stream);
+
+/* Y = (X . W_virtual) * alpha (+ bias[N], fp32, may be NULL) (+ ReLU with RZ_FLAG_RELU).
+   Replaces rz_linear_forward_tl, python/rz_linear/impl/RzLinearForward.py:6-85, and the separate
+   bias add of python/rz_linear/RzLinear.py:93-94.  `shadow` may be NULL only on the SIMT path. */
+int rz_linear_forward(const rz_problem *pb, const void *X, const float *hashed, const void *shadow,
+                      const float *bias, void *Y, void *stream);
+
+/* dX = (dY . W_virtual^T) * alpha.
+   Replaces rz_linear_backward_input_grad_tl, python/rz_linear/impl/RzLinearBackward.py:374-449. */
+int rz_linear_backward_input(const rz_problem *pb, const void *dY, const float *hashed,
+                             const void *shadow, void *dX, void *stream);
+
+/* dH[offset(pk,pn) + r*BN + c] += (X^T . dY)[pk*BK + r, pn*BN + c] * alpha; dH is zeroed first
+   unless RZ_FLAG_ACCUMULATE_DH.  Replaces rz_linear_backward_weight_grad_tl,
+   python/rz_linear/impl/RzLinearBackward.py:23-97. */
+int rz_linear_backward_weight(const rz_problem *pb, const void *X, const void *dY, float *dH,
+                              void *stream);
+
+/* W[K,N] (fp32) = gather of the hashed slices.
+   Replaces rz_linear_idx_tl, python/rz_linear/impl/RzLinearIdx.py:6-45. */
+int rz_linear_materialize(const rz_problem *pb, const float *hashed, float *W, void *stream);
+
+/* hashed -= lr * dH, and (when shadow != NULL) the shadow copies are rewritten in the same pass.
+   No counterpart in the reference (its optimiser step is torch's); used by the data-parallel step. */
+int rz_sgd_step(const rz_problem *pb, float *hashed, const float *dH, float lr, void *shadow,
+                void *stream);
+
+/* Reads and clears the device-side status word (synchronises the device).  *out = RZ_OK or
+   RZ_ERR_PIPELINE; *detail (may be NULL) receives the code of the wait that gave up. */
+int rz_device_status(int *out, int *detail);
+
+/* Number of kernels this library has launched in this process (all threads). */
+uint64_t rz_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RZLINEAR_B200_H */

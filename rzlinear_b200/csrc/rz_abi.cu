@@ -1,0 +1,248 @@
+// C ABI of librzlinear_b200.so: argument validation, path selection and dispatch.
+// Declarations and the reference interfaces they replace: include/rzlinear_b200.h.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "rz_common.h"
+
+namespace {
+
+thread_local char g_cuda_error[256] = "";
+std::atomic<uint64_t> g_launches{0};
+
+// Device-side status word: 0, or (wait code << 8 | 1) once a bounded wait gave up.
+__device__ int g_rz_status_word = 0;
+
+int validate(const rz_problem *pb)
+{
+    if (!pb) return RZ_ERR_NULL;
+    if (pb->M <= 0 || pb->K <= 0 || pb->N <= 0 || pb->H <= 0 || pb->BK <= 0 || pb->BN <= 0) return RZ_ERR_SHAPE;
+    const int64_t lim = (int64_t)1 << 31;
+    if (pb->M >= lim || pb->K >= lim || pb->N >= lim || pb->H >= lim) return RZ_ERR_SHAPE;
+    if ((int64_t)pb->BK * pb->BN >= lim) return RZ_ERR_SHAPE;
+    if (pb->H <= (int64_t)pb->BK * pb->BN) return RZ_ERR_HASH_RANGE;
+    if (pb->hash_mode != RZ_HASH_SINGLE && pb->hash_mode != RZ_HASH_TWO_LEVEL) return RZ_ERR_HASH_PARAM;
+    if (pb->R[0] <= 0) return RZ_ERR_HASH_PARAM;
+    for (int i = 0; i < 8; ++i)
+        if (pb->R[i] < 0 || pb->R[i] >= lim) return RZ_ERR_HASH_PARAM;
+    if (pb->io_dtype != RZ_F32 && pb->io_dtype != RZ_BF16) return RZ_ERR_DTYPE;
+    if (pb->precision != RZ_PREC_FP32 && pb->precision != RZ_PREC_TF32 && pb->precision != RZ_PREC_BF16)
+        return RZ_ERR_DTYPE;
+    if (pb->precision == RZ_PREC_TF32 && pb->io_dtype != RZ_F32) return RZ_ERR_DTYPE;
+    if (pb->precision == RZ_PREC_BF16 && pb->io_dtype != RZ_BF16) return RZ_ERR_DTYPE;
+    return RZ_OK;
+}
+
+RzHash make_hash(const rz_problem *pb)
+{
+    RzHash h;
+    h.R0 = (uint64_t)pb->R[0];
+    h.R1 = (uint64_t)pb->R[1];
+    h.R2 = (uint64_t)pb->R[2];
+    h.R3 = (uint64_t)pb->R[3];
+    h.R4 = (uint64_t)pb->R[4];
+    h.R5 = (uint64_t)pb->R[5];
+    h.R7 = (uint64_t)pb->R[7];
+    h.range = (uint64_t)(pb->H - (int64_t)pb->BK * pb->BN);
+    h.BK = pb->BK;
+    h.BN = pb->BN;
+    h.two_level = pb->hash_mode == RZ_HASH_TWO_LEVEL;
+    h.pad = 0;
+    rz_hash_finish(h);
+    return h;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool use_tc(const rz_problem *pb, int op)
+{
+    if (pb->flags & RZ_FLAG_FORCE_SIMT) return false;
+    if (pb->precision == RZ_PREC_FP32) return false;
+    return rz_tc_supported(pb, op);
+}
+
+RzLaunchCtx make_ctx(const rz_problem *pb, void *stream)
+{
+    RzLaunchCtx c;
+    c.pb = pb;
+    c.hash = make_hash(pb);
+    c.stream = reinterpret_cast<cudaStream_t>(stream);
+    return c;
+}
+
+}  // namespace
+
+int rz_record_cuda(cudaError_t e, const char *what)
+{
+    if (e == cudaSuccess) return RZ_OK;
+    snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", what, cudaGetErrorString(e));
+    return RZ_ERR_CUDA;
+}
+
+void rz_count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+int *rz_device_status_word()
+{
+    int *p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_rz_status_word) != cudaSuccess) return nullptr;
+    return p;
+}
+
+extern "C" {
+
+int rz_version(void) { return 100; }
+
+const char *rz_status_string(int status)
+{
+    switch (status) {
+    case RZ_OK: return "ok";
+    case RZ_ERR_NULL: return "a required pointer is NULL";
+    case RZ_ERR_SHAPE: return "bad shape: a dimension is <= 0 or does not fit";
+    case RZ_ERR_HASH_RANGE: return "hashed array too small: H must be larger than BK*BN";
+    case RZ_ERR_DTYPE: return "unsupported io_dtype / precision combination";
+    case RZ_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case RZ_ERR_HASH_PARAM: return "bad hash parameters (prime <= 0, negative or >= 2^31 random number, unknown mode)";
+    case RZ_ERR_CUDA: return "CUDA call failed";
+    case RZ_ERR_PIPELINE: return "device pipeline wait timed out";
+    case RZ_ERR_UNSUPPORTED: return "problem not supported on the requested path";
+    case RZ_ERR_TOO_LARGE: return "size exceeds the capacity of this entry point";
+    default: return "unknown status";
+    }
+}
+
+const char *rz_last_cuda_error(void) { return g_cuda_error; }
+
+int rz_hash_indices_host(const rz_problem *pb, int64_t *out_host)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!out_host) return RZ_ERR_NULL;
+    RzHash h = make_hash(pb);
+    const uint32_t nk = (uint32_t)((pb->K + pb->BK - 1) / pb->BK);
+    const uint32_t nn = (uint32_t)((pb->N + pb->BN - 1) / pb->BN);
+    for (uint32_t pk = 0; pk < nk; ++pk)
+        for (uint32_t pn = 0; pn < nn; ++pn) out_host[(size_t)pk * nn + pn] = (int64_t)rz_tile_offset(h, pk, pn);
+    return RZ_OK;
+}
+
+int rz_hash_indices_device(const rz_problem *pb, int64_t *out_dev, void *stream)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!out_dev) return RZ_ERR_NULL;
+    return rz_simt_hash_indices(make_ctx(pb, stream), out_dev);
+}
+
+int rz_plan(const rz_problem *pb, int op)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (op < RZ_OP_FORWARD || op > RZ_OP_BACKWARD_WEIGHT) return RZ_ERR_UNSUPPORTED;
+    return use_tc(pb, op) ? RZ_PATH_TCGEN05 : RZ_PATH_SIMT;
+}
+
+size_t rz_shadow_bytes(const rz_problem *pb)
+{
+    if (validate(pb)) return 0;
+    if (!use_tc(pb, RZ_OP_FORWARD) && !use_tc(pb, RZ_OP_BACKWARD_INPUT)) return 0;
+    return rz_tc_shadow_bytes(pb);
+}
+
+int rz_shadow_refresh(const rz_problem *pb, const float *hashed, void *shadow, void *stream)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (rz_shadow_bytes(pb) == 0) return RZ_OK;
+    if (!hashed || !shadow) return RZ_ERR_NULL;
+    if (!aligned16(hashed) || (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
+    return rz_tc_shadow_refresh(make_ctx(pb, stream), hashed, shadow);
+}
+
+int rz_linear_forward(const rz_problem *pb, const void *X, const float *hashed, const void *shadow,
+                      const float *bias, void *Y, void *stream)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!X || !hashed || !Y) return RZ_ERR_NULL;
+    RzLaunchCtx c = make_ctx(pb, stream);
+    if (use_tc(pb, RZ_OP_FORWARD)) {
+        if (!shadow) return RZ_ERR_NULL;
+        if (!aligned16(X) || !aligned16(Y) || (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
+        return rz_tc_forward(c, X, shadow, bias, Y);
+    }
+    return rz_simt_forward(c, X, hashed, bias, Y);
+}
+
+int rz_linear_backward_input(const rz_problem *pb, const void *dY, const float *hashed, const void *shadow,
+                             void *dX, void *stream)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!dY || !hashed || !dX) return RZ_ERR_NULL;
+    RzLaunchCtx c = make_ctx(pb, stream);
+    if (use_tc(pb, RZ_OP_BACKWARD_INPUT)) {
+        if (!shadow) return RZ_ERR_NULL;
+        if (!aligned16(dY) || !aligned16(dX) || (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
+        return rz_tc_backward_input(c, dY, shadow, dX);
+    }
+    return rz_simt_backward_input(c, dY, hashed, dX);
+}
+
+int rz_linear_backward_weight(const rz_problem *pb, const void *X, const void *dY, float *dH, void *stream)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!X || !dY || !dH) return RZ_ERR_NULL;
+    RzLaunchCtx c = make_ctx(pb, stream);
+    if (!(pb->flags & RZ_FLAG_ACCUMULATE_DH)) {
+        st = rz_record_cuda(cudaMemsetAsync(dH, 0, sizeof(float) * (size_t)pb->H, c.stream), "zero dH");
+        if (st) return st;
+    }
+    if (use_tc(pb, RZ_OP_BACKWARD_WEIGHT)) {
+        if (!aligned16(X) || !aligned16(dY) || !aligned16(dH)) return RZ_ERR_ALIGN;
+        return rz_tc_backward_weight(c, X, dY, dH);
+    }
+    return rz_simt_backward_weight(c, X, dY, dH);
+}
+
+int rz_linear_materialize(const rz_problem *pb, const float *hashed, float *W, void *stream)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!hashed || !W) return RZ_ERR_NULL;
+    return rz_simt_materialize(make_ctx(pb, stream), hashed, W);
+}
+
+int rz_sgd_step(const rz_problem *pb, float *hashed, const float *dH, float lr, void *shadow, void *stream)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!hashed || !dH) return RZ_ERR_NULL;
+    if (!aligned16(hashed) || !aligned16(dH)) return RZ_ERR_ALIGN;
+    if (shadow && rz_shadow_bytes(pb) == 0) shadow = nullptr;
+    if (shadow && (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
+    return rz_tc_sgd_step(make_ctx(pb, stream), hashed, dH, lr, shadow);
+}
+
+int rz_device_status(int *out, int *detail)
+{
+    if (!out) return RZ_ERR_NULL;
+    int word = 0;
+    int st = rz_record_cuda(cudaDeviceSynchronize(), "device synchronize");
+    if (st) return st;
+    st = rz_record_cuda(cudaMemcpyFromSymbol(&word, g_rz_status_word, sizeof(int)), "read status word");
+    if (st) return st;
+    if (word != 0) {
+        int zero = 0;
+        st = rz_record_cuda(cudaMemcpyToSymbol(g_rz_status_word, &zero, sizeof(int)), "clear status word");
+        if (st) return st;
+    }
+    *out = word ? RZ_ERR_PIPELINE : RZ_OK;
+    if (detail) *detail = word >> 8;
+    return RZ_OK;
+}
+
+uint64_t rz_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

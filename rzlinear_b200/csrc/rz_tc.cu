@@ -1,0 +1,684 @@
+// Tensor-core (tcgen05 + TMEM + TMA) kernels of the RzLinear path for sm_100a.
+//
+// One persistent, warp-specialised kernel template covers the three contractions:
+//   OP_FWD  Y [M,N] = X  [M,K] . W[K,N]      A = X tile  (K-major),  B = W slice (N-major)
+//   OP_DX   dX[M,K] = dY [M,N] . W[K,N]^T    A = dY tile (K-major),  B = W slice (K-major)
+//   OP_DW   dH     += X^T[K,M] . dY[M,N]     A = X tile  (M-major),  B = dY tile (N-major)
+// A CTA owns a 128 x 256 output block; the accumulator lives in TMEM (two 256-column buffers so
+// the epilogue of one block overlaps the main loop of the next).  Warp 0 produces (TMA loads into
+// a 4-stage ring of 128-byte-swizzled shared-memory tiles), warp 1 issues tcgen05.mma, warps 2-5
+// drain TMEM: they scale/bias/convert and store (FWD, DX) or scatter-add into the hashed gradient
+// with warp-wide coalesced reductions (DW).
+//
+// The virtual weight is never materialised.  For every pipeline stage the producer warp computes
+// the hash-tile offsets in registers and TMA-loads the matching rows of the slice.  TMA needs a
+// 16-byte aligned start, and a slice starts at any element, so FWD and DX read a "shadow" of the
+// hashed array: NS element-shifted copies in the compute type (NS = 8 bf16 / 4 tf32); the copy
+// whose shift equals offset mod NS holds the slice at an aligned position.  The shadow tensor map
+// is 3-D {element, slice row (stride BN), copy}.
+//
+// No multicast, no cluster, no peer memory.  Every mbarrier wait is bounded: a wait that runs out
+// records a code in the device status word and all roles leave their loops, the producer waits
+// for its loads in flight, the MMA thread for its MMAs, TMEM is freed and the kernel returns.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "rz_common.h"
+#include "rz_ptx.cuh"
+
+using namespace rzptx;
+
+namespace {
+
+constexpr int OP_FWD = 0, OP_DX = 1, OP_DW = 2;
+
+constexpr int TILE_R = 128;  // MMA M
+constexpr int TILE_C = 256;  // MMA N
+constexpr int STAGES = 4;
+constexpr int A_BYTES = 16384;
+constexpr int B_BYTES = 32768;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NTHREADS = 192;
+constexpr int BATCH = 8;     // pipeline stages per hash batch of the producer warp
+constexpr int MAX_TPS = 8;   // B boxes per stage at most
+constexpr int GROUP_ROWS = 16;
+
+constexpr int SMEM_EPI = 4 * 32 * 33 * 4;
+constexpr int SMEM_TABLE = 3 * BATCH * MAX_TPS * 4;
+constexpr int SMEM_BARS = (2 * STAGES + 5) * 8;
+constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + SMEM_EPI + SMEM_TABLE + SMEM_BARS + 16 + 1024;
+
+struct TcParams {
+    RzHash hash;
+    uint32_t M, K, N;
+    uint32_t rows, cols;        // output block grid extents (elements)
+    uint32_t tiles_r, tiles_c;
+    uint32_t nchunks;           // pipeline stages along the whole contraction
+    uint32_t nsplit, chunks_per_split;
+    uint32_t total_items;
+    uint32_t br;                // OP_DX: slice rows per B box
+    uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;  // descriptor strides, bytes
+    uint32_t idesc;
+    float alpha;
+    int relu;
+    const float *bias;
+    void *out;
+    float *dH;
+    int *status;
+    long long wait_limit;
+};
+
+__device__ __forceinline__ void wait_cycles(uint32_t bar, uint32_t parity, long long cycles)
+{
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > cycles) break;
+}
+
+template <int OP, bool TF32>
+__global__ void __launch_bounds__(NTHREADS, 1)
+rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
+{
+    constexpr int ES = TF32 ? 4 : 2;        // operand element size
+    constexpr int EPR = 128 / ES;           // elements per 128-byte swizzle row
+    constexpr int KC = EPR;                 // contraction elements per stage
+    constexpr int NS = 16 / ES;             // shifted shadow copies
+    constexpr int MMAS = 4;                 // tcgen05.mma per stage (K = 16 bf16 / 8 tf32 each)
+    constexpr int ATOM = KC * 128;          // bytes of one 128-byte-wide column block of an MN-major tile
+    constexpr int A_ATOMS = TILE_R / EPR;
+    constexpr int B_ATOMS = TILE_C / EPR;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    float *epi_scratch = reinterpret_cast<float *>(smem_gen + STAGES * STAGE_BYTES);
+    uint32_t *tab_x = reinterpret_cast<uint32_t *>(smem_gen + STAGES * STAGE_BYTES + SMEM_EPI);
+    uint32_t *tab_y = tab_x + BATCH * MAX_TPS;
+    uint32_t *tab_z = tab_y + BATCH * MAX_TPS;
+    const uint32_t bars = smem_base + STAGES * STAGE_BYTES + SMEM_EPI + SMEM_TABLE;
+    const uint32_t bar_full = bars;                       // [STAGES]
+    const uint32_t bar_empty = bars + 8 * STAGES;         // [STAGES]
+    const uint32_t bar_tfull = bars + 16 * STAGES;        // [2]
+    const uint32_t bar_tempty = bars + 16 * STAGES + 16;  // [2]
+    const uint32_t bar_drain = bars + 16 * STAGES + 32;   // [1]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + STAGES * STAGE_BYTES + SMEM_EPI + SMEM_TABLE + SMEM_BARS);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_tfull + 8 * b, 1);
+            mbar_init(bar_tempty + 8 * b, 4);
+        }
+        mbar_init(bar_drain, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+        tma_prefetch_desc(&mapA);
+        tma_prefetch_desc(&mapB);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+
+    bool ok = true;
+
+    // decode a work item into its output block and contraction range
+    auto decode = [&](uint32_t item, uint32_t &tr, uint32_t &tc, uint32_t &c_begin, uint32_t &c_end) {
+        uint32_t tile = item / p.nsplit, split = item - tile * p.nsplit;
+        uint32_t per_group = GROUP_ROWS * p.tiles_c;
+        uint32_t group = tile / per_group, within = tile - group * per_group;
+        uint32_t first_r = group * GROUP_ROWS;
+        uint32_t gsz = min(p.tiles_r - first_r, (uint32_t)GROUP_ROWS);
+        tr = first_r + within % gsz;
+        tc = within / gsz;
+        c_begin = split * p.chunks_per_split;
+        c_end = min(p.nchunks, c_begin + p.chunks_per_split);
+    };
+
+    if (warp == 0) {
+        // ===================== producer =====================
+        uint32_t it = 0;  // stages armed so far
+        for (uint32_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x) {
+            uint32_t tr, tc, c_begin, c_end;
+            decode(item, tr, tc, c_begin, c_end);
+            for (uint32_t cb = c_begin; cb < c_end && ok; cb += BATCH) {
+                const uint32_t nb = min((uint32_t)BATCH, c_end - cb);
+                if (OP != OP_DW) {
+                    const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS : (uint32_t)TILE_C / p.br;
+                    for (uint32_t e = lane; e < nb * tps; e += 32) {
+                        const uint32_t ci = e / tps, j = e - ci * tps;
+                        uint32_t pk, pn, x_in, y_in;
+                        if (OP == OP_FWD) {
+                            const uint32_t k0 = (cb + ci) * KC, n = tc * TILE_C + j * EPR;
+                            pk = k0 / (uint32_t)p.hash.BK;
+                            y_in = k0 - pk * (uint32_t)p.hash.BK;
+                            pn = n / (uint32_t)p.hash.BN;
+                            x_in = n - pn * (uint32_t)p.hash.BN;
+                        } else {
+                            const uint32_t n0 = (cb + ci) * KC, ko = tc * TILE_C + j * p.br;
+                            pn = n0 / (uint32_t)p.hash.BN;
+                            x_in = n0 - pn * (uint32_t)p.hash.BN;
+                            pk = ko / (uint32_t)p.hash.BK;
+                            y_in = ko - pk * (uint32_t)p.hash.BK;
+                        }
+                        const uint32_t off = (uint32_t)rz_tile_offset(p.hash, pk, pn);
+                        const uint32_t sh = off & (NS - 1);
+                        tab_x[ci * MAX_TPS + j] = off - sh + x_in;
+                        tab_y[ci * MAX_TPS + j] = y_in;
+                        tab_z[ci * MAX_TPS + j] = sh;
+                    }
+                    __syncwarp();
+                }
+                if (lane == 0) {
+                    for (uint32_t ci = 0; ci < nb; ++ci) {
+                        const uint32_t g = it + ci, s = g % STAGES, ph = (g / STAGES) & 1;
+                        if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1, RZ_WAIT_SMEM_EMPTY, p.status, p.wait_limit)) {
+                            ok = false;
+                            it += ci;
+                            break;
+                        }
+                        const uint32_t full = bar_full + 8 * s;
+                        const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+                        mbar_arrive_expect_tx(full, STAGE_BYTES);
+                        const uint32_t d0 = (cb + ci) * KC;  // contraction start of this stage
+                        if (OP == OP_FWD || OP == OP_DX) {
+                            tma_load_2d(sa, &mapA, full, (int32_t)d0, (int32_t)(tr * TILE_R));
+                            const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS : (uint32_t)TILE_C / p.br;
+                            const uint32_t box_bytes = (OP == OP_FWD) ? (uint32_t)ATOM : p.br * 128u;
+                            for (uint32_t j = 0; j < tps; ++j)
+                                tma_load_3d(sb + j * box_bytes, &mapB, full, (int32_t)tab_x[ci * MAX_TPS + j],
+                                            (int32_t)tab_y[ci * MAX_TPS + j], (int32_t)tab_z[ci * MAX_TPS + j]);
+                        } else {
+#pragma unroll
+                            for (int a = 0; a < A_ATOMS; ++a)
+                                tma_load_2d(sa + a * ATOM, &mapA, full, (int32_t)(tr * TILE_R + a * EPR), (int32_t)d0);
+#pragma unroll
+                            for (int j = 0; j < B_ATOMS; ++j)
+                                tma_load_2d(sb + j * ATOM, &mapB, full, (int32_t)(tc * TILE_C + j * EPR), (int32_t)d0);
+                        }
+                    }
+                    if (ok) it += nb;
+                }
+                __syncwarp();
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                it = __shfl_sync(0xffffffffu, it, 0);
+            }
+        }
+        if (!ok && lane == 0) {
+            // give the loads already issued time to land before the CTA retires
+            const uint32_t lo = it > STAGES ? it - STAGES : 0;
+            for (uint32_t g = lo; g < it; ++g) wait_cycles(bar_full + 8 * (g % STAGES), (g / STAGES) & 1, 4000000);
+        }
+    } else if (warp == 1) {
+        // ===================== MMA issuer =====================
+        uint32_t it = 0, n_items = 0;
+        for (uint32_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x, ++n_items) {
+            uint32_t tr, tc, c_begin, c_end;
+            decode(item, tr, tc, c_begin, c_end);
+            const uint32_t buf = n_items & 1, tph = (n_items >> 1) & 1;
+            if (lane == 0) {
+                if (!mbar_wait_bounded(bar_tempty + 8 * buf, tph ^ 1, RZ_WAIT_TMEM_EMPTY, p.status, p.wait_limit)) ok = false;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * TILE_C;
+                for (uint32_t c = c_begin; c < c_end && ok; ++c, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(bar_full + 8 * s, ph, RZ_WAIT_SMEM_FULL, p.status, p.wait_limit)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < MMAS; ++kk) {
+                        const uint64_t ad = make_desc_sw128(sa + kk * p.a_kstep, p.a_lbo, p.a_sbo);
+                        const uint64_t bd = make_desc_sw128(sb + kk * p.b_kstep, p.b_lbo, p.b_sbo);
+                        tc_mma<TF32>(d_tmem, ad, bd, p.idesc, (c > c_begin || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty + 8 * s);
+                }
+                if (ok) tc_commit(bar_tfull + 8 * buf);
+            }
+            __syncwarp();
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            it = __shfl_sync(0xffffffffu, it, 0);
+        }
+        if (!ok && lane == 0) {
+            // MMAs may still be running: wait (bounded) until the tensor core has drained
+            tc_commit(bar_drain);
+            wait_cycles(bar_drain, 0, 20000000);
+        }
+    } else {
+        // ===================== epilogue =====================
+        const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
+        float *scratch = epi_scratch + q * (32 * 33);
+        uint32_t n_items = 0;
+        for (uint32_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x, ++n_items) {
+            uint32_t tr, tc, c_begin, c_end;
+            decode(item, tr, tc, c_begin, c_end);
+            const uint32_t buf = n_items & 1, tph = (n_items >> 1) & 1;
+            bool mine = mbar_wait_bounded(bar_tfull + 8 * buf, tph, RZ_WAIT_TMEM_FULL, p.status, p.wait_limit);
+            ok = __all_sync(0xffffffffu, mine);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t row = tr * TILE_R + q * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < TILE_C / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + buf * TILE_C + c * 32, v);
+                tmem_ld_wait();
+                const uint32_t col = tc * TILE_C + c * 32;
+                if (OP == OP_DW) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) scratch[lane * 33 + j] = __uint_as_float(v[j]) * p.alpha;
+                    __syncwarp();
+                    const uint32_t kb = tr * TILE_R + q * 32;
+                    if (kb < p.K && col < p.N) {
+                        const uint32_t pk = kb / (uint32_t)p.hash.BK, pn = col / (uint32_t)p.hash.BN;
+                        float *dst = p.dH + rz_tile_offset(p.hash, pk, pn) +
+                                     (uint64_t)(kb - pk * (uint32_t)p.hash.BK) * (uint32_t)p.hash.BN +
+                                     (col - pn * (uint32_t)p.hash.BN) + lane;
+                        const bool col_ok = col + lane < p.N;
+                        const uint32_t nrow = min(32u, p.K - kb);
+                        for (uint32_t rr = 0; rr < nrow; ++rr)
+                            if (col_ok) atomicAdd(dst + (size_t)rr * (uint32_t)p.hash.BN, scratch[rr * 33 + lane]);
+                    }
+                    __syncwarp();
+                } else if (row < p.rows && col < p.cols) {
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+                    if (OP == OP_FWD) {
+                        if (p.bias) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < p.cols) f[j] += __ldg(p.bias + col + j);
+                        }
+                        if (p.relu) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
+                        }
+                    }
+                    if (TF32) {
+                        float4 *o = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + (size_t)row * p.cols + col);
+#pragma unroll
+                        for (int g = 0; g < 8; ++g)
+                            if (col + g * 4 < p.cols) o[g] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
+                    } else {
+                        uint4 *o = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + (size_t)row * p.cols + col);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (col + g * 8 < p.cols) {
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(f[8 * g + 0], f[8 * g + 1]);
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(f[8 * g + 2], f[8 * g + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(f[8 * g + 4], f[8 * g + 5]);
+                                __nv_bfloat162 h3 = __floats2bfloat162_rn(f[8 * g + 6], f[8 * g + 7]);
+                                uint4 u;
+                                u.x = *reinterpret_cast<uint32_t *>(&h0);
+                                u.y = *reinterpret_cast<uint32_t *>(&h1);
+                                u.z = *reinterpret_cast<uint32_t *>(&h2);
+                                u.w = *reinterpret_cast<uint32_t *>(&h3);
+                                o[g] = u;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- shadow copies and SGD -----------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t to_tf32(float v)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+
+// copy s, element j  =  convert(hashed[j + s])   (0 past the end); one thread writes NS elements of every copy
+template <bool TF32>
+__global__ void rz_shadow_kernel(const float *__restrict__ hashed, uint8_t *__restrict__ shadow, uint32_t H, uint32_t Hc,
+                                 size_t copy_stride)
+{
+    constexpr int NS = TF32 ? 4 : 8;
+    const uint32_t groups = Hc / NS;
+    for (uint32_t g = blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += gridDim.x * blockDim.x) {
+        const uint32_t j0 = g * NS;
+        float v[2 * NS];
+#pragma unroll
+        for (int i = 0; i < 2 * NS; ++i) v[i] = (j0 + i < H) ? hashed[j0 + i] : 0.f;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            uint4 u;
+            if (TF32) {
+                u.x = to_tf32(v[s + 0]);
+                u.y = to_tf32(v[s + 1]);
+                u.z = to_tf32(v[s + 2]);
+                u.w = to_tf32(v[s + 3]);
+            } else {
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[s + 0], v[s + 1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[s + 2], v[s + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[s + 4], v[s + 5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[s + 6], v[s + 7]);
+                u.x = *reinterpret_cast<uint32_t *>(&h0);
+                u.y = *reinterpret_cast<uint32_t *>(&h1);
+                u.z = *reinterpret_cast<uint32_t *>(&h2);
+                u.w = *reinterpret_cast<uint32_t *>(&h3);
+            }
+            *reinterpret_cast<uint4 *>(shadow + s * copy_stride + (size_t)g * 16) = u;
+        }
+    }
+}
+
+__global__ void rz_sgd_kernel(float *__restrict__ hashed, const float *__restrict__ dH, float lr, uint32_t H)
+{
+    const uint32_t n4 = H / 4;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+        float4 h = reinterpret_cast<float4 *>(hashed)[i];
+        const float4 g = reinterpret_cast<const float4 *>(dH)[i];
+        h.x -= lr * g.x;
+        h.y -= lr * g.y;
+        h.z -= lr * g.z;
+        h.w -= lr * g.w;
+        reinterpret_cast<float4 *>(hashed)[i] = h;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (H & 3u)) {
+        const uint32_t i = n4 * 4 + threadIdx.x;
+        hashed[i] -= lr * dH[i];
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+struct Geometry {
+    int es, epr, ns;
+    uint32_t Hc;
+    size_t copy_stride;
+};
+
+Geometry geometry(const rz_problem *pb)
+{
+    Geometry g;
+    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    g.es = tf32 ? 4 : 2;
+    g.epr = 128 / g.es;
+    g.ns = 16 / g.es;
+    g.Hc = (uint32_t)((pb->H + 63) / 64 * 64);
+    g.copy_stride = ((size_t)g.Hc * g.es + 255) / 256 * 256;
+    return g;
+}
+
+int encode(CUtensorMap *map, bool tf32, void *base, int rank, const uint64_t *dims, const uint64_t *strides_bytes,
+           const uint32_t *box)
+{
+    EncodeTiledFn fn = get_encode();
+    if (!fn) return rz_record_cuda(cudaErrorUnknown, "cuTensorMapEncodeTiled not available");
+    cuuint64_t gdim[3];
+    cuuint64_t gstr[2];
+    cuuint32_t bx[3], estr[3];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bx[i] = box[i];
+        estr[i] = 1;
+    }
+    for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+    CUresult r = fn(map, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, base,
+                    gdim, gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char msg[96];
+        snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed (CUresult %d, rank %d)", (int)r, rank);
+        return rz_record_cuda(cudaErrorInvalidValue, msg);
+    }
+    return RZ_OK;
+}
+
+int num_sms()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+uint32_t env_u32(const char *name, uint32_t dflt)
+{
+    const char *s = getenv(name);
+    return s ? (uint32_t)strtoul(s, nullptr, 0) : dflt;
+}
+
+template <int OP, bool TF32>
+int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p)
+{
+    const rz_problem *pb = c.pb;
+    constexpr int ES = TF32 ? 4 : 2;
+    constexpr int EPR = 128 / ES;
+    constexpr int KC = EPR;
+    p.hash = c.hash;
+    p.M = (uint32_t)pb->M;
+    p.K = (uint32_t)pb->K;
+    p.N = (uint32_t)pb->N;
+    p.rows = (OP == OP_DW) ? p.K : p.M;
+    p.cols = (OP == OP_DX) ? p.K : p.N;
+    const uint32_t depth = (OP == OP_FWD) ? p.K : (OP == OP_DX ? p.N : p.M);
+    p.tiles_r = (p.rows + TILE_R - 1) / TILE_R;
+    p.tiles_c = (p.cols + TILE_C - 1) / TILE_C;
+    p.nchunks = (depth + KC - 1) / KC;
+    const int sms = num_sms();
+    const uint32_t tiles = p.tiles_r * p.tiles_c;
+    p.nsplit = 1;
+    if (OP == OP_DW && tiles < (uint32_t)sms) {
+        // split the batch so that every SM gets work; each split adds into dH independently
+        uint32_t want = ((uint32_t)sms + tiles - 1) / tiles;
+        uint32_t max_split = (p.nchunks + 7) / 8;  // at least 8 stages per split
+        if (max_split < 1) max_split = 1;
+        p.nsplit = want < max_split ? want : max_split;
+    }
+    p.chunks_per_split = (p.nchunks + p.nsplit - 1) / p.nsplit;
+    p.nsplit = (p.nchunks + p.chunks_per_split - 1) / p.chunks_per_split;
+    p.total_items = tiles * p.nsplit;
+    p.alpha = pb->alpha;
+    p.relu = (pb->flags & RZ_FLAG_RELU) ? 1 : 0;
+    p.status = rz_device_status_word();
+    if (!p.status) return rz_record_cuda(cudaErrorUnknown, "status word address");
+    p.wait_limit = 2000000000ll;
+
+    // shared-memory descriptors (bytes)
+    const uint32_t atom = KC * 128;
+    const uint32_t mn_kstep = (TF32 ? 8 : 16) * 128;  // contraction rows per MMA x 128-byte rows
+    if (OP == OP_FWD) {
+        p.a_lbo = 16, p.a_sbo = 1024, p.a_kstep = 32;           // K-major
+        p.b_lbo = atom, p.b_sbo = 1024, p.b_kstep = mn_kstep;   // N-major
+    } else if (OP == OP_DX) {
+        p.a_lbo = 16, p.a_sbo = 1024, p.a_kstep = 32;
+        p.b_lbo = 16, p.b_sbo = 1024, p.b_kstep = 32;
+    } else {
+        p.a_lbo = atom, p.a_sbo = 1024, p.a_kstep = mn_kstep;
+        p.b_lbo = atom, p.b_sbo = 1024, p.b_kstep = mn_kstep;
+    }
+    const uint32_t a_major = (OP == OP_DW) ? 1u : 0u, b_major = (OP == OP_DX) ? 0u : 1u;
+    const uint32_t fmt = TF32 ? 2u : 1u;
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (a_major << 15) | (b_major << 16) | ((uint32_t)(TILE_C >> 3) << 17) |
+              ((uint32_t)(TILE_R >> 4) << 24);
+
+    // bring-up overrides of the descriptor strides
+    p.a_lbo = env_u32("RZ_TC_A_LBO", p.a_lbo);
+    p.a_sbo = env_u32("RZ_TC_A_SBO", p.a_sbo);
+    p.a_kstep = env_u32("RZ_TC_A_KSTEP", p.a_kstep);
+    p.b_lbo = env_u32("RZ_TC_B_LBO", p.b_lbo);
+    p.b_sbo = env_u32("RZ_TC_B_SBO", p.b_sbo);
+    p.b_kstep = env_u32("RZ_TC_B_KSTEP", p.b_kstep);
+    p.idesc = env_u32("RZ_TC_IDESC", p.idesc);
+
+    auto kern = rz_tc_kernel<OP, TF32>;
+    int st = rz_record_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL),
+                            "set max dynamic shared memory");
+    if (st) return st;
+    const uint32_t grid = p.total_items < (uint32_t)sms ? p.total_items : (uint32_t)sms;
+    kern<<<grid, NTHREADS, SMEM_TOTAL, c.stream>>>(mapA, mapB, p);
+    rz_count_launch(1);
+    return rz_record_cuda(cudaGetLastError(), "tcgen05 kernel launch");
+}
+
+// 2-D map over a row-major matrix [rows][cols] of the operand type
+int map_matrix(CUtensorMap *map, bool tf32, const void *base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows)
+{
+    const int es = tf32 ? 4 : 2;
+    uint64_t dims[2] = {cols, rows};
+    uint64_t strides[1] = {cols * (uint64_t)es};
+    uint32_t box[2] = {box_cols, box_rows};
+    return encode(map, tf32, const_cast<void *>(base), 2, dims, strides, box);
+}
+
+// 3-D map over the shadow: {element of a copy, slice row (stride BN elements), copy}
+int map_shadow(CUtensorMap *map, const rz_problem *pb, const void *shadow, uint32_t box_rows)
+{
+    const Geometry g = geometry(pb);
+    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    uint64_t dims[3] = {g.Hc, (uint64_t)pb->BK, (uint64_t)g.ns};
+    uint64_t strides[2] = {(uint64_t)pb->BN * g.es, (uint64_t)g.copy_stride};
+    uint32_t box[3] = {(uint32_t)g.epr, box_rows, 1};
+    return encode(map, tf32, const_cast<void *>(shadow), 3, dims, strides, box);
+}
+
+}  // namespace
+
+bool rz_tc_supported(const rz_problem *pb, int op)
+{
+    (void)op;
+    if (pb->precision != RZ_PREC_TF32 && pb->precision != RZ_PREC_BF16) return false;
+    const Geometry g = geometry(pb);
+    if (pb->BK % g.epr || pb->BN % g.epr) return false;
+    if (pb->BK <= 256 ? (256 % pb->BK != 0) : (pb->BK % 256 != 0)) return false;
+    if ((pb->K * g.es) % 16 || (pb->N * g.es) % 16) return false;
+    if (pb->M < TILE_R || pb->K < g.epr || pb->N < g.epr) return false;  // TMA boxes no larger than the matrices
+    return true;
+}
+
+size_t rz_tc_shadow_bytes(const rz_problem *pb)
+{
+    const Geometry g = geometry(pb);
+    return g.copy_stride * (size_t)g.ns;
+}
+
+int rz_tc_shadow_refresh(const RzLaunchCtx &c, const float *hashed, void *shadow)
+{
+    const Geometry g = geometry(c.pb);
+    const uint32_t groups = g.Hc / g.ns;
+    uint32_t blocks = (groups + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (c.pb->precision == RZ_PREC_TF32)
+        rz_shadow_kernel<true><<<blocks, 256, 0, c.stream>>>(hashed, (uint8_t *)shadow, (uint32_t)c.pb->H, g.Hc, g.copy_stride);
+    else
+        rz_shadow_kernel<false><<<blocks, 256, 0, c.stream>>>(hashed, (uint8_t *)shadow, (uint32_t)c.pb->H, g.Hc, g.copy_stride);
+    rz_count_launch(1);
+    return rz_record_cuda(cudaGetLastError(), "shadow refresh launch");
+}
+
+int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float lr, void *shadow)
+{
+    const uint32_t H = (uint32_t)c.pb->H;
+    uint32_t blocks = (H / 4 + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    rz_sgd_kernel<<<blocks, 256, 0, c.stream>>>(hashed, dH, lr, H);
+    rz_count_launch(1);
+    int st = rz_record_cuda(cudaGetLastError(), "sgd launch");
+    if (st || !shadow) return st;
+    return rz_tc_shadow_refresh(c, hashed, shadow);
+}
+
+int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const float *bias, void *Y)
+{
+    const rz_problem *pb = c.pb;
+    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    const Geometry g = geometry(pb);
+    CUtensorMap mapA, mapB;
+    int st = map_matrix(&mapA, tf32, X, pb->M, pb->K, g.epr, TILE_R);
+    if (st) return st;
+    st = map_shadow(&mapB, pb, shadow, g.epr);
+    if (st) return st;
+    TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.bias = bias;
+    p.out = Y;
+    return tf32 ? launch_tc<OP_FWD, true>(c, mapA, mapB, p) : launch_tc<OP_FWD, false>(c, mapA, mapB, p);
+}
+
+int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shadow, void *dX)
+{
+    const rz_problem *pb = c.pb;
+    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    const Geometry g = geometry(pb);
+    CUtensorMap mapA, mapB;
+    int st = map_matrix(&mapA, tf32, dY, pb->M, pb->N, g.epr, TILE_R);
+    if (st) return st;
+    const uint32_t br = pb->BK < 256 ? (uint32_t)pb->BK : 256u;
+    st = map_shadow(&mapB, pb, shadow, br);
+    if (st) return st;
+    TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.br = br;
+    p.out = dX;
+    return tf32 ? launch_tc<OP_DX, true>(c, mapA, mapB, p) : launch_tc<OP_DX, false>(c, mapA, mapB, p);
+}
+
+int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, float *dH)
+{
+    const rz_problem *pb = c.pb;
+    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    const Geometry g = geometry(pb);
+    CUtensorMap mapA, mapB;
+    int st = map_matrix(&mapA, tf32, X, pb->M, pb->K, g.epr, g.epr);
+    if (st) return st;
+    st = map_matrix(&mapB, tf32, dY, pb->M, pb->N, g.epr, g.epr);
+    if (st) return st;
+    TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.dH = dH;
+    return tf32 ? launch_tc<OP_DW, true>(c, mapA, mapB, p) : launch_tc<OP_DW, false>(c, mapA, mapB, p);
+}
