@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""Benchmark of the RzLinear hot path on B200: one data-parallel training step of a single layer.
+
+Workload (the multi-GPU configuration of the baseline): global X[131072, 8192] bf16 ~ N(0,1) sharded
+on rows over the ranks, one RzLinear with a virtual W[8192, 8192] drawn from a replicated fp32
+hashed array of 2^22 elements (BK = BN = 128, single-level hash, prime 2038074743), dY ~ N(0,1).
+A step = forward + hashed-weight gradient + all-reduce of that 16 MiB gradient (N > 1) +
+input gradient + SGD update of the hashed array (which also rewrites the tensor-core shadow).
+The global batch is fixed, so scaling is "strong": every rank does 1/N of the work.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is virtual-dense TFLOP/s of the whole job (6*M*K*N per step) with
+the shards resident in HBM; `e2e` is the same step fed from pinned host memory with the copies
+timed; `roofline` is the dominant kernel against the measured bf16 tensor peak; `cpu_baseline` is
+the materialised-weight computation (the CPU oracle) on a bounded sample.  `--impl reference`
+times that CPU path alone.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+PRIME = 2038074743
+M_GLOBAL, K, N, H, BK, BN = 131072, 8192, 8192, 1 << 22, 128, 128
+LR = 1e-4
+METRIC = "fwd+bwd virtual-dense TFLOP/s (whole job)"
+WORKLOAD = "dp_train_step X[131072,8192]bf16 W_virtual[8192,8192] H=2^22 BK=BN=128"
+
+
+def seeded_R(seed=1005):
+    rs = np.random.RandomState(seed)
+    return [PRIME] + [int(v) for v in rs.randint(1, 2**31 - 1, 3)] + [0, 0, 0, 0]
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                pr = torch.cuda.get_device_properties(self.index)
+                bus = f"{pr.pci_domain_id:08X}:{pr.pci_bus_id:02X}:{pr.pci_device_id:02X}.0"
+                h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            names = {
+                pynvml.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                pynvml.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                pynvml.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                pynvml.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            }
+            while not self._stop_evt.is_set():
+                self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                try:
+                    mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    for bit, name in names.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+                time.sleep(0.05)
+        except Exception as e:  # NVML missing: report what we know
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+_CPU_STEP = {}
+
+
+def cpu_reference_step(Ms: int, threads: int, repeats: int = 1):
+    """The reference's materialised-weight computation on the host (oracle.MaterializedStep: fp32, torch's
+    multi-threaded CPU kernels): gather W, Y = X@W, dX = dY@W^T, dH = index_add of X^T@dY.
+    Returns the best seconds per pass over Ms rows."""
+    from oracle import rz_oracle as o
+    torch.set_num_threads(threads)
+    if "step" not in _CPU_STEP:
+        _CPU_STEP["step"] = o.MaterializedStep(K, N, H, BK, BN, seeded_R())
+    g = torch.Generator().manual_seed(1005)
+    X = torch.randn(Ms, K, generator=g).bfloat16().float()
+    dY = torch.randn(Ms, N, generator=g).bfloat16().float()
+    h = (torch.rand(H, generator=g) * 2 - 1) / 90.5
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        _CPU_STEP["step"].run(X, dY, h)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    Ms = 4096
+    cpu_reference_step(256, threads)  # warm the thread pool and page in
+    times = []
+    for i in range(args.warmup + args.steps):
+        t = cpu_reference_step(Ms, threads)
+        if i >= args.warmup:
+            times.append(t)
+    sec = sum(times) / len(times)
+    tflops = 6.0 * Ms * K * N / sec / 1e12
+    sample = f"{Ms} of {M_GLOBAL} rows per step (gather W + 3 fp32 GEMMs + index_add), {threads} threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m-global", type=int, default=M_GLOBAL, help="override the global batch (profiling small cases)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    from rzlinear_b200 import _lib
+    from rzlinear_b200.dist import RzDataParallelStep, shard_rows
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path for the product kernels)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+
+    m_global = args.m_global
+    lo, hi = shard_rows(m_global, rank, world)
+    M = hi - lo
+    R = seeded_R()
+    step = RzDataParallelStep(M, K, N, H, BK, BN, R, _lib.HASH_SINGLE, torch.bfloat16, LR, dev)
+    assert _lib.plan(step.pb, 0) == _lib.PATH_TCGEN05
+
+    # synthetic shard, generated on the device in slabs (seeded per rank), resident before timing starts
+    g = torch.Generator(device=dev).manual_seed(1005 + rank)
+    X = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+    dY = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    for r0 in range(0, M, 8192):
+        r1 = min(M, r0 + 8192)
+        X[r0:r1] = torch.randn((r1 - r0, K), generator=g, device=dev, dtype=torch.float32).bfloat16()
+        dY[r0:r1] = torch.randn((r1 - r0, N), generator=g, device=dev, dtype=torch.float32).bfloat16()
+    hg = torch.Generator().manual_seed(1005)
+    h0 = (torch.rand(H, generator=hg) * 2 - 1) / 90.5
+    step.load_weights(h0.to(dev))
+    torch.cuda.synchronize()
+
+    names = ["forward", "backward_weight", "backward_input", "sgd"]
+    events = []
+
+    def marks_for(slot):
+        def mark(name):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            slot.append((name, ev))
+        return mark
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step.step(X, dY)
+    barrier()
+    launches0 = _lib.launch_count()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for _ in range(args.steps):
+        slot = []
+        step.step(X, dY, marks_for(slot))
+        events.append(slot)
+    t_end.record()
+    barrier()
+    clocks = sampler.stop()
+    launches = _lib.launch_count() - launches0
+    st, detail = _lib.device_status()
+    assert st == 0, f"device pipeline status {st} (wait code {detail})"
+    ms_total = t_start.elapsed_time(t_end)
+
+    per_kernel = {n: 0.0 for n in names}
+    for slot in events:
+        for (n0, e0), (n1, e1) in zip(slot[:-1], slot[1:]):
+            per_kernel[n1] += e0.elapsed_time(e1)
+    per_kernel = {n: v / args.steps for n, v in per_kernel.items()}
+
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    flops_step = 6.0 * m_global * K * N
+    value = flops_step / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: the same step fed from pinned host buffers, copies inside the timed region ----
+    e2e = None
+    if not args.no_e2e:
+        Xh = torch.empty((M, K), dtype=torch.bfloat16).pin_memory()
+        dYh = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+        Xh.copy_(X)
+        dYh.copy_(dY)
+        hh = torch.empty(H, dtype=torch.float32).pin_memory()
+        torch.cuda.synchronize()
+        e_steps = max(2, min(args.steps, 5))
+        for _ in range(2):
+            step.step_host(Xh, dYh, hh)
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e_steps):
+            step.step_host(Xh, dYh, hh)
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        ms_e2e = float(te.item()) / e_steps
+        e2e = {"value": flops_step / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(Xh.numel() * 2 + dYh.numel() * 2), "d2h_bytes_per_step": int(H * 4),
+               "ms_per_step": ms_e2e, "steps": e_steps,
+               "api": "RzDataParallelStep.step_host(X_pinned, dY_pinned, hashed_out_pinned)"}
+        del Xh, dYh
+
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        dom = max(("forward", "backward_weight", "backward_input"), key=lambda n: per_kernel[n])
+        flops_kernel = 2.0 * M * K * N
+        achieved = flops_kernel / (per_kernel[dom] * 1e-3) / 1e12
+        peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+        roofline = {"bound": "tensor", "kernel": f"rz_tc_kernel<{dom}>", "achieved": achieved, "peak": peak,
+                    "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                    "peak_source": f"{peak_kind} bf16_tflops_sustained (kernel timed inside a long step)",
+                    "ms_per_launch": per_kernel[dom]}
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD if m_global == M_GLOBAL else WORKLOAD + f" (m_global={m_global})",
+                       "rows_per_gpu": M, "parallelism": f"dp{world}",
+                       "l2": "inputs larger than L2 (X and dY shards are >= 256 MiB each)"},
+            "per_gpu_tflops": value / world,
+            "kernel_ms": per_kernel,
+            "kernel_tflops": {n: flops_kernel / (per_kernel[n] * 1e-3) / 1e12
+                              for n in ("forward", "backward_weight", "backward_input")},
+            "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches),
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if world == 1 and not args.no_cpu:
+            threads = os.cpu_count() or 1
+            Ms = 4096
+            cpu_reference_step(256, threads)
+            sec = cpu_reference_step(Ms, threads, repeats=2)
+            line["cpu_baseline"] = {
+                "value": 6.0 * Ms * K * N / sec / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"{Ms} of {m_global} rows, best of 2 (gather W + 3 fp32 GEMMs + index_add)"}
+        print(json.dumps(line), flush=True)
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -156,19 +156,23 @@ __device__ __forceinline__ void tmem_ld_wait()
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
-//   K-major  : rows of 128 bytes along the contraction; sbo = bytes between 8-row groups (1024 when
-//              rows are packed); lbo is not used by the hardware for swizzled K-major operands.
-//   MN-major : rows of 128 bytes along M/N, one row per contraction index; sbo = bytes between
-//              groups of 8 contraction rows, lbo = bytes between 128-byte-wide column blocks.
-__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+// Shared-memory matrix descriptor for 128-byte-swizzled tiles, descriptor version 1.
+//   layout 2 (128-byte swizzle, 16-byte chunks), K-major : rows of 128 bytes along the contraction;
+//              sbo = bytes between 8-row groups (1024 when rows are packed); lbo unused.
+//   layout 2, MN-major (16-bit types) : rows of 128 bytes along M/N, one row per contraction index;
+//              sbo = bytes between groups of 8 contraction rows, lbo = bytes between 128-byte-wide
+//              column blocks.
+//   layout 1 (128-byte swizzle, 32-byte chunks) : the only layout MN-major 32-bit (tf32) operands
+//              may use; as above but the contraction rows group by 4 (sbo = 512 when packed).
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                    uint32_t layout = 2)
 {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
+    d |= (uint64_t)layout << 61;
     return d;
 }
 

@@ -59,6 +59,7 @@ struct TcParams {
     uint32_t total_items;
     uint32_t br;                // OP_DX: slice rows per B box
     uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;  // descriptor strides, bytes
+    uint32_t a_layout, b_layout;                            // descriptor swizzle layout type
     uint32_t idesc;
     float alpha;
     int relu;
@@ -240,8 +241,8 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
 #pragma unroll
                     for (int kk = 0; kk < MMAS; ++kk) {
-                        const uint64_t ad = make_desc_sw128(sa + kk * p.a_kstep, p.a_lbo, p.a_sbo);
-                        const uint64_t bd = make_desc_sw128(sb + kk * p.b_kstep, p.b_lbo, p.b_sbo);
+                        const uint64_t ad = make_desc_sw128(sa + kk * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
+                        const uint64_t bd = make_desc_sw128(sb + kk * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
                         tc_mma<TF32>(d_tmem, ad, bd, p.idesc, (c > c_begin || kk > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty + 8 * s);
@@ -447,8 +448,10 @@ Geometry geometry(const rz_problem *pb)
     return g;
 }
 
-int encode(CUtensorMap *map, bool tf32, void *base, int rank, const uint64_t *dims, const uint64_t *strides_bytes,
-           const uint32_t *box)
+// `mn_major`: the tile feeds an M/N-major operand; for 32-bit elements that needs the 32-byte-chunk flavour
+// of the 128-byte swizzle, every other case uses the 16-byte-chunk one.
+int encode(CUtensorMap *map, bool tf32, bool mn_major, void *base, int rank, const uint64_t *dims,
+           const uint64_t *strides_bytes, const uint32_t *box)
 {
     EncodeTiledFn fn = get_encode();
     if (!fn) return rz_record_cuda(cudaErrorUnknown, "cuTensorMapEncodeTiled not available");
@@ -462,7 +465,8 @@ int encode(CUtensorMap *map, bool tf32, void *base, int rank, const uint64_t *di
     }
     for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
     CUresult r = fn(map, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, base,
-                    gdim, gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    gdim, gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    (tf32 && mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         char msg[96];
@@ -530,15 +534,20 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     // shared-memory descriptors (bytes)
     const uint32_t atom = KC * 128;
     const uint32_t mn_kstep = (TF32 ? 8 : 16) * 128;  // contraction rows per MMA x 128-byte rows
+    const uint32_t mn_sbo = TF32 ? 512 : 1024;        // tf32 M/N-major: rows group by 4 (32-byte-chunk swizzle)
+    const uint32_t mn_layout = TF32 ? 1 : 2;
+    p.a_layout = p.b_layout = 2;
     if (OP == OP_FWD) {
-        p.a_lbo = 16, p.a_sbo = 1024, p.a_kstep = 32;           // K-major
-        p.b_lbo = atom, p.b_sbo = 1024, p.b_kstep = mn_kstep;   // N-major
+        p.a_lbo = 16, p.a_sbo = 1024, p.a_kstep = 32;             // K-major
+        p.b_lbo = atom, p.b_sbo = mn_sbo, p.b_kstep = mn_kstep;   // N-major
+        p.b_layout = mn_layout;
     } else if (OP == OP_DX) {
         p.a_lbo = 16, p.a_sbo = 1024, p.a_kstep = 32;
         p.b_lbo = 16, p.b_sbo = 1024, p.b_kstep = 32;
     } else {
-        p.a_lbo = atom, p.a_sbo = 1024, p.a_kstep = mn_kstep;
-        p.b_lbo = atom, p.b_sbo = 1024, p.b_kstep = mn_kstep;
+        p.a_lbo = atom, p.a_sbo = mn_sbo, p.a_kstep = mn_kstep;
+        p.b_lbo = atom, p.b_sbo = mn_sbo, p.b_kstep = mn_kstep;
+        p.a_layout = p.b_layout = mn_layout;
     }
     const uint32_t a_major = (OP == OP_DW) ? 1u : 0u, b_major = (OP == OP_DX) ? 0u : 1u;
     const uint32_t fmt = TF32 ? 2u : 1u;
@@ -565,24 +574,25 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
 }
 
 // 2-D map over a row-major matrix [rows][cols] of the operand type
-int map_matrix(CUtensorMap *map, bool tf32, const void *base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows)
+int map_matrix(CUtensorMap *map, bool tf32, bool mn_major, const void *base, uint64_t rows, uint64_t cols,
+               uint32_t box_cols, uint32_t box_rows)
 {
     const int es = tf32 ? 4 : 2;
     uint64_t dims[2] = {cols, rows};
     uint64_t strides[1] = {cols * (uint64_t)es};
     uint32_t box[2] = {box_cols, box_rows};
-    return encode(map, tf32, const_cast<void *>(base), 2, dims, strides, box);
+    return encode(map, tf32, mn_major, const_cast<void *>(base), 2, dims, strides, box);
 }
 
 // 3-D map over the shadow: {element of a copy, slice row (stride BN elements), copy}
-int map_shadow(CUtensorMap *map, const rz_problem *pb, const void *shadow, uint32_t box_rows)
+int map_shadow(CUtensorMap *map, const rz_problem *pb, bool mn_major, const void *shadow, uint32_t box_rows)
 {
     const Geometry g = geometry(pb);
     const bool tf32 = pb->precision == RZ_PREC_TF32;
     uint64_t dims[3] = {g.Hc, (uint64_t)pb->BK, (uint64_t)g.ns};
     uint64_t strides[2] = {(uint64_t)pb->BN * g.es, (uint64_t)g.copy_stride};
     uint32_t box[3] = {(uint32_t)g.epr, box_rows, 1};
-    return encode(map, tf32, const_cast<void *>(shadow), 3, dims, strides, box);
+    return encode(map, tf32, mn_major, const_cast<void *>(shadow), 3, dims, strides, box);
 }
 
 }  // namespace
@@ -638,9 +648,9 @@ int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const
     const bool tf32 = pb->precision == RZ_PREC_TF32;
     const Geometry g = geometry(pb);
     CUtensorMap mapA, mapB;
-    int st = map_matrix(&mapA, tf32, X, pb->M, pb->K, g.epr, TILE_R);
+    int st = map_matrix(&mapA, tf32, false, X, pb->M, pb->K, g.epr, TILE_R);
     if (st) return st;
-    st = map_shadow(&mapB, pb, shadow, g.epr);
+    st = map_shadow(&mapB, pb, true, shadow, g.epr);
     if (st) return st;
     TcParams p;
     memset(&p, 0, sizeof(p));
@@ -655,10 +665,10 @@ int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shado
     const bool tf32 = pb->precision == RZ_PREC_TF32;
     const Geometry g = geometry(pb);
     CUtensorMap mapA, mapB;
-    int st = map_matrix(&mapA, tf32, dY, pb->M, pb->N, g.epr, TILE_R);
+    int st = map_matrix(&mapA, tf32, false, dY, pb->M, pb->N, g.epr, TILE_R);
     if (st) return st;
     const uint32_t br = pb->BK < 256 ? (uint32_t)pb->BK : 256u;
-    st = map_shadow(&mapB, pb, shadow, br);
+    st = map_shadow(&mapB, pb, false, shadow, br);
     if (st) return st;
     TcParams p;
     memset(&p, 0, sizeof(p));
@@ -673,9 +683,9 @@ int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, f
     const bool tf32 = pb->precision == RZ_PREC_TF32;
     const Geometry g = geometry(pb);
     CUtensorMap mapA, mapB;
-    int st = map_matrix(&mapA, tf32, X, pb->M, pb->K, g.epr, g.epr);
+    int st = map_matrix(&mapA, tf32, true, X, pb->M, pb->K, g.epr, g.epr);
     if (st) return st;
-    st = map_matrix(&mapB, tf32, dY, pb->M, pb->N, g.epr, g.epr);
+    st = map_matrix(&mapB, tf32, true, dY, pb->M, pb->N, g.epr, g.epr);
     if (st) return st;
     TcParams p;
     memset(&p, 0, sizeof(p));
