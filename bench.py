@@ -157,6 +157,7 @@ def main():
     ap.add_argument("--m-global", type=int, default=M_GLOBAL, help="override the global batch (profiling small cases)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-cublas", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -278,6 +279,36 @@ def main():
                "api": "RzDataParallelStep.step_host(X_pinned, dY_pinned, hashed_out_pinned)"}
         del Xh, dYh
 
+    # ---- cuBLAS dense GEMMs of the same virtual shape, same run, same clocks (rank 0) ----
+    cublas = None
+    if rank == 0 and not args.no_cublas:
+        Wd = (torch.randn((K, N), device=dev, dtype=torch.float32) / 90.5).bfloat16()
+        dWd = torch.empty((K, N), dtype=torch.bfloat16, device=dev)
+        gemms = {"forward": lambda: torch.matmul(X, Wd, out=step.Y),
+                 "backward_input": lambda: torch.matmul(dY, Wd.t(), out=step.dX),
+                 "backward_weight": lambda: torch.matmul(X.t(), dY, out=dWd)}
+        cublas_ms = {}
+        for name, fn in gemms.items():
+            for _ in range(3):
+                fn()
+            c0 = torch.cuda.Event(enable_timing=True)
+            c1 = torch.cuda.Event(enable_timing=True)
+            reps = max(3, min(args.steps, 10))
+            c0.record()
+            for _ in range(reps):
+                fn()
+            c1.record()
+            torch.cuda.synchronize()
+            cublas_ms[name] = c0.elapsed_time(c1) / reps
+        tot = sum(cublas_ms.values())
+        ours = per_kernel["forward"] + per_kernel["backward_weight"] + per_kernel["backward_input"]
+        cublas = {"ms": cublas_ms, "tflops": {n: 2.0 * M * K * N / (v * 1e-3) / 1e12 for n, v in cublas_ms.items()},
+                  "fwd_bwd_tflops": 6.0 * M * K * N / (tot * 1e-3) / 1e12,
+                  "ours_fwd_bwd_tflops": 6.0 * M * K * N / (ours * 1e-3) / 1e12,
+                  "ours_pct_of_cublas": 100.0 * tot / ours,
+                  "what": "torch.matmul bf16 on a dense W[K,N]: X@W, dY@W^T, X^T@dY, back to back per GEMM"}
+        del Wd, dWd
+
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         dom = max(("forward", "backward_weight", "backward_input"), key=lambda n: per_kernel[n])
@@ -303,6 +334,8 @@ def main():
         }
         if e2e is not None:
             line["e2e"] = e2e
+        if cublas is not None:
+            line["cublas"] = cublas
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
             Ms = 4096
