@@ -105,6 +105,20 @@ int rz_shadow_refresh(const rz_problem *pb, const float *hashed, void *shadow, v
 int rz_linear_forward(const rz_problem *pb, const void *X, const float *hashed, const void *shadow,
                       const float *bias, void *Y, void *stream);
 
+/* Forward pass for callers that cannot supply scratch memory.  No counterpart in the reference.
+   Same result as rz_linear_forward, but the shadow copies live in a fixed 16 MiB array inside the
+   library instead of a caller-allocated buffer, and the call allocates nothing.  Meant for hosts that
+   have no way to allocate device memory at this point: all of HBM already belongs to their own pool,
+   they sit behind a binding that only passes pointers, or they cannot afford the device-wide stall an
+   allocation may cause.  Limits: the problem's shadow (rz_shadow_bytes) must fit
+   RZ_NOALLOC_SCRATCH_BYTES, i.e. H <= 2^20, else RZ_ERR_TOO_LARGE; the array is rewritten by
+   every call and shared by all callers on a device, so calls that may overlap on the GPU race (order
+   them on one stream or with events); the first call on each device resolves the array's address and
+   should be made before any stream capture starts. */
+#define RZ_NOALLOC_SCRATCH_BYTES ((size_t)16 << 20)
+int rz_linear_forward_noalloc(const rz_problem *pb, const void *X, const float *hashed,
+                              const float *bias, void *Y, void *stream);
+
 /* dX = (dY . W_virtual^T) * alpha.
    Replaces rz_linear_backward_input_grad_tl, python/rz_linear/impl/RzLinearBackward.py:374-449. */
 int rz_linear_backward_input(const rz_problem *pb, const void *dY, const float *hashed,

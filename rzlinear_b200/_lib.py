@@ -215,3 +215,20 @@ def device_status():
 
 def launch_count() -> int:
     return int(load().rz_launch_count())
+
+
+NOALLOC_SCRATCH_BYTES = 16 << 20
+
+
+def forward_noalloc(pb, x, hashed, bias, y) -> None:
+    """rz_linear_forward_noalloc: forward pass whose scratch is a fixed array inside the library.
+
+    For hosts that cannot allocate device memory when they call (see include/rzlinear_b200.h for who
+    that is and for the limits: shadow <= NOALLOC_SCRATCH_BYTES, one shared array per device, calls
+    that overlap on the GPU race, first call per device before any stream capture)."""
+    _require_cuda(x, hashed, bias, y)
+    fn = load().rz_linear_forward_noalloc
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.POINTER(RzProblem)] + [ctypes.c_void_p] * 5
+    with torch.cuda.device(x.device):
+        check(fn(ctypes.byref(pb), _ptr(x), _ptr(hashed), _ptr(bias), _ptr(y), _stream(x.device)))
