@@ -4,11 +4,15 @@
 //   OP_FWD  Y [M,N] = X  [M,K] . W[K,N]      A = X tile  (K-major),  B = W slice (N-major)
 //   OP_DX   dX[M,K] = dY [M,N] . W[K,N]^T    A = dY tile (K-major),  B = W slice (K-major)
 //   OP_DW   dH     += X^T[K,M] . dY[M,N]     A = X tile  (M-major),  B = dY tile (N-major)
-// A CTA owns a 128 x 256 output block; the accumulator lives in TMEM (two 256-column buffers so
-// the epilogue of one block overlaps the main loop of the next).  Warp 0 produces (TMA loads into
-// a 4-stage ring of 128-byte-swizzled shared-memory tiles), warp 1 issues tcgen05.mma, warps 2-5
-// drain TMEM: they scale/bias/convert and store (FWD, DX) or scatter-add into the hashed gradient
-// with warp-wide coalesced reductions (DW).
+// CTAS = 1: a CTA owns a 128 x 256 output block (tcgen05.mma cta_group::1, M = 128).
+// CTAS = 2: two CTAs of a cluster own a 256 x 256 block (cta_group::2, M = 256): each CTA stages its
+//           128 rows of A and its 128 columns of B, so every SM pulls 32 KB instead of 48 KB from L2
+//           per pipeline stage, which is what bounds the 1-CTA kernel.  The leader CTA (rank 0)
+//           issues the MMAs for both; barriers that gate them live in the leader.
+// The accumulator lives in TMEM (two 256-column buffers, so the epilogue of one block overlaps the
+// main loop of the next).  Warp 0 produces (TMA loads into a ring of 128-byte-swizzled shared-memory
+// tiles), warp 1 issues tcgen05.mma, warps 2-5 drain TMEM: they scale/bias/convert and store (FWD, DX)
+// or scatter-add into the hashed gradient with warp-wide coalesced reductions (DW).
 //
 // The virtual weight is never materialised.  For every pipeline stage the producer warp computes
 // the hash-tile offsets in registers and TMA-loads the matching rows of the slice.  TMA needs a
@@ -17,9 +21,10 @@
 // whose shift equals offset mod NS holds the slice at an aligned position.  The shadow tensor map
 // is 3-D {element, slice row (stride BN), copy}.
 //
-// No multicast, no cluster, no peer memory.  Every mbarrier wait is bounded: a wait that runs out
-// records a code in the device status word and all roles leave their loops, the producer waits
-// for its loads in flight, the MMA thread for its MMAs, TMEM is freed and the kernel returns.
+// Every TMA load is a plain per-CTA copy of this GPU's memory; no kernel touches peer-GPU memory.
+// Every mbarrier wait is bounded: a wait that runs out records a code in the device status word and
+// all roles leave their loops, the producer waits for its loads in flight, the MMA thread for its
+// MMAs, TMEM is freed and the kernel returns.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -33,31 +38,43 @@ namespace {
 
 constexpr int OP_FWD = 0, OP_DX = 1, OP_DW = 2;
 
-constexpr int TILE_R = 128;  // MMA M
+constexpr int TILE_R = 128;  // rows per CTA (MMA M = 128 * CTAS)
 constexpr int TILE_C = 256;  // MMA N
-constexpr int STAGES = 4;
 constexpr int A_BYTES = 16384;
-constexpr int B_BYTES = 32768;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NTHREADS = 192;
 constexpr int BATCH = 8;     // pipeline stages per hash batch of the producer warp
 constexpr int MAX_TPS = 8;   // B boxes per stage at most
-constexpr int GROUP_ROWS = 16;
+constexpr int GROUP_ROWS = 8;
 
+// Shared-memory budget (227 KB per CTA): the operand ring takes what the other parts leave.
+// Only the weight-gradient epilogue needs transpose scratch, so FWD / DX get one more 32 KB stage.
 constexpr int SMEM_EPI = 4 * 32 * 33 * 4;
 constexpr int SMEM_TABLE = 3 * BATCH * MAX_TPS * 4;
-constexpr int SMEM_BARS = (2 * STAGES + 5) * 8;
-constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + SMEM_EPI + SMEM_TABLE + SMEM_BARS + 16 + 1024;
+constexpr int MAX_STAGES = 7;
+constexpr int SMEM_BARS = (2 * MAX_STAGES + 5) * 8;
+constexpr int SMEM_LIMIT = 232448;
+__host__ __device__ constexpr int smem_epi(int op) { return op == OP_DW ? SMEM_EPI : 0; }
+__host__ __device__ constexpr int stage_bytes(int ctas) { return A_BYTES + (TILE_C / ctas) * 128; }
+__host__ __device__ constexpr int num_stages(int op, int ctas)
+{
+    int n = (SMEM_LIMIT - 1024 - 16 - SMEM_BARS - SMEM_TABLE - smem_epi(op)) / stage_bytes(ctas);
+    return n > MAX_STAGES ? MAX_STAGES : n;
+}
+__host__ __device__ constexpr int smem_total(int op, int ctas)
+{
+    return num_stages(op, ctas) * stage_bytes(ctas) + smem_epi(op) + SMEM_TABLE + SMEM_BARS + 16 + 1024;
+}
 
 struct TcParams {
     RzHash hash;
     uint32_t M, K, N;
-    uint32_t rows, cols;        // output block grid extents (elements)
+    uint32_t rows, cols;        // output extents (elements)
     uint32_t tiles_r, tiles_c;
     uint32_t nchunks;           // pipeline stages along the whole contraction
     uint32_t nsplit, chunks_per_split;
     uint32_t total_items;
     uint32_t br;                // OP_DX: slice rows per B box
+    uint32_t group_rows;        // row tiles per rasterisation group
     uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;  // descriptor strides, bytes
     uint32_t a_layout, b_layout;                            // descriptor swizzle layout type
     uint32_t idesc;
@@ -77,7 +94,7 @@ __device__ __forceinline__ void wait_cycles(uint32_t bar, uint32_t parity, long 
         if (clock64() - t0 > cycles) break;
 }
 
-template <int OP, bool TF32>
+template <int OP, bool TF32, int CTAS>
 __global__ void __launch_bounds__(NTHREADS, 1)
 rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
@@ -87,25 +104,37 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     constexpr int NS = 16 / ES;             // shifted shadow copies
     constexpr int MMAS = 4;                 // tcgen05.mma per stage (K = 16 bf16 / 8 tf32 each)
     constexpr int ATOM = KC * 128;          // bytes of one 128-byte-wide column block of an MN-major tile
+    constexpr int B_COLS = TILE_C / CTAS;   // columns of B this CTA stages
+    constexpr int B_BYTES = B_COLS * 128;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int STAGES = num_stages(OP, CTAS);
+    constexpr int SMEM_RING = STAGES * STAGE_BYTES;
+    constexpr int SMEM_EPI_OP = smem_epi(OP);
+    static_assert(STAGE_BYTES == stage_bytes(CTAS), "stage size");
     constexpr int A_ATOMS = TILE_R / EPR;
-    constexpr int B_ATOMS = TILE_C / EPR;
+    constexpr int B_ATOMS = B_COLS / EPR;
+    constexpr int PAIR_R = TILE_R * CTAS;   // rows of a work item
+    static_assert(STAGES <= MAX_STAGES, "barrier storage");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    float *epi_scratch = reinterpret_cast<float *>(smem_gen + STAGES * STAGE_BYTES);
-    uint32_t *tab_x = reinterpret_cast<uint32_t *>(smem_gen + STAGES * STAGE_BYTES + SMEM_EPI);
+    float *epi_scratch = reinterpret_cast<float *>(smem_gen + SMEM_RING);
+    uint32_t *tab_x = reinterpret_cast<uint32_t *>(smem_gen + SMEM_RING + SMEM_EPI_OP);
     uint32_t *tab_y = tab_x + BATCH * MAX_TPS;
     uint32_t *tab_z = tab_y + BATCH * MAX_TPS;
-    const uint32_t bars = smem_base + STAGES * STAGE_BYTES + SMEM_EPI + SMEM_TABLE;
-    const uint32_t bar_full = bars;                       // [STAGES]
-    const uint32_t bar_empty = bars + 8 * STAGES;         // [STAGES]
-    const uint32_t bar_tfull = bars + 16 * STAGES;        // [2]
-    const uint32_t bar_tempty = bars + 16 * STAGES + 16;  // [2]
-    const uint32_t bar_drain = bars + 16 * STAGES + 32;   // [1]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + STAGES * STAGE_BYTES + SMEM_EPI + SMEM_TABLE + SMEM_BARS);
+    const uint32_t bars = smem_base + SMEM_RING + SMEM_EPI_OP + SMEM_TABLE;
+    const uint32_t bar_full = bars;                           // [STAGES]  used in the leader CTA
+    const uint32_t bar_empty = bars + 8 * MAX_STAGES;         // [STAGES]  one set per CTA
+    const uint32_t bar_tfull = bars + 16 * MAX_STAGES;        // [2]       one set per CTA
+    const uint32_t bar_tempty = bars + 16 * MAX_STAGES + 16;  // [2]       used in the leader CTA
+    const uint32_t bar_drain = bars + 16 * MAX_STAGES + 32;   // [1]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + SMEM_RING + SMEM_EPI_OP + SMEM_TABLE + SMEM_BARS);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = (CTAS == 2) ? cluster_ctarank() : 0u;   // 0 = leader
+    const uint32_t first_item = (CTAS == 2) ? cluster_id_x() : blockIdx.x;
+    const uint32_t item_stride = gridDim.x / CTAS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -114,7 +143,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_tfull + 8 * b, 1);
-            mbar_init(bar_tempty + 8 * b, 4);
+            mbar_init(bar_tempty + 8 * b, 4 * CTAS);
         }
         mbar_init(bar_drain, 1);
         fence_barrier_init();
@@ -123,11 +152,17 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         tma_prefetch_desc(&mapB);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
-        tmem_relinquish();
+        if (CTAS == 2) {
+            tmem_alloc_pair(smem_u32(tmem_slot), 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(tmem_slot), 512);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CTAS == 2) cluster_sync_all();   // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
 
@@ -136,10 +171,10 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     // decode a work item into its output block and contraction range
     auto decode = [&](uint32_t item, uint32_t &tr, uint32_t &tc, uint32_t &c_begin, uint32_t &c_end) {
         uint32_t tile = item / p.nsplit, split = item - tile * p.nsplit;
-        uint32_t per_group = GROUP_ROWS * p.tiles_c;
+        uint32_t per_group = p.group_rows * p.tiles_c;
         uint32_t group = tile / per_group, within = tile - group * per_group;
-        uint32_t first_r = group * GROUP_ROWS;
-        uint32_t gsz = min(p.tiles_r - first_r, (uint32_t)GROUP_ROWS);
+        uint32_t first_r = group * p.group_rows;
+        uint32_t gsz = min(p.tiles_r - first_r, p.group_rows);
         tr = first_r + within % gsz;
         tc = within / gsz;
         c_begin = split * p.chunks_per_split;
@@ -147,26 +182,31 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     };
 
     if (warp == 0) {
-        // ===================== producer =====================
+        // ===================== producer (both CTAs of a pair) =====================
         uint32_t it = 0;  // stages armed so far
-        for (uint32_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x) {
+        // transaction bytes of a stage are counted on the leader's barrier
+        uint32_t full_base = bar_full;
+        if (CTAS == 2) full_base = mapa_cluster(bar_full, 0);
+        for (uint32_t item = first_item; item < p.total_items && ok; item += item_stride) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
+            const uint32_t row0 = tr * PAIR_R + rank * TILE_R;     // first output row staged by this CTA (A)
+            const uint32_t col0 = tc * TILE_C + rank * B_COLS;     // first output column staged by this CTA (B)
             for (uint32_t cb = c_begin; cb < c_end && ok; cb += BATCH) {
                 const uint32_t nb = min((uint32_t)BATCH, c_end - cb);
                 if (OP != OP_DW) {
-                    const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS : (uint32_t)TILE_C / p.br;
+                    const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS : (uint32_t)B_COLS / p.br;
                     for (uint32_t e = lane; e < nb * tps; e += 32) {
                         const uint32_t ci = e / tps, j = e - ci * tps;
                         uint32_t pk, pn, x_in, y_in;
                         if (OP == OP_FWD) {
-                            const uint32_t k0 = (cb + ci) * KC, n = tc * TILE_C + j * EPR;
+                            const uint32_t k0 = (cb + ci) * KC, n = col0 + j * EPR;
                             pk = k0 / (uint32_t)p.hash.BK;
                             y_in = k0 - pk * (uint32_t)p.hash.BK;
                             pn = n / (uint32_t)p.hash.BN;
                             x_in = n - pn * (uint32_t)p.hash.BN;
                         } else {
-                            const uint32_t n0 = (cb + ci) * KC, ko = tc * TILE_C + j * p.br;
+                            const uint32_t n0 = (cb + ci) * KC, ko = col0 + j * p.br;
                             pn = n0 / (uint32_t)p.hash.BN;
                             x_in = n0 - pn * (uint32_t)p.hash.BN;
                             pk = ko / (uint32_t)p.hash.BK;
@@ -188,24 +228,32 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                             it += ci;
                             break;
                         }
-                        const uint32_t full = bar_full + 8 * s;
+                        const uint32_t full = full_base + 8 * s;
                         const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
-                        mbar_arrive_expect_tx(full, STAGE_BYTES);
+                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, STAGE_BYTES * CTAS);
                         const uint32_t d0 = (cb + ci) * KC;  // contraction start of this stage
                         if (OP == OP_FWD || OP == OP_DX) {
-                            tma_load_2d(sa, &mapA, full, (int32_t)d0, (int32_t)(tr * TILE_R));
-                            const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS : (uint32_t)TILE_C / p.br;
+                            if (CTAS == 2) tma_load_2d_pair(sa, &mapA, full, (int32_t)d0, (int32_t)row0);
+                            else tma_load_2d(sa, &mapA, full, (int32_t)d0, (int32_t)row0);
+                            const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS : (uint32_t)B_COLS / p.br;
                             const uint32_t box_bytes = (OP == OP_FWD) ? (uint32_t)ATOM : p.br * 128u;
-                            for (uint32_t j = 0; j < tps; ++j)
-                                tma_load_3d(sb + j * box_bytes, &mapB, full, (int32_t)tab_x[ci * MAX_TPS + j],
-                                            (int32_t)tab_y[ci * MAX_TPS + j], (int32_t)tab_z[ci * MAX_TPS + j]);
+                            for (uint32_t j = 0; j < tps; ++j) {
+                                const int32_t x = (int32_t)tab_x[ci * MAX_TPS + j], y = (int32_t)tab_y[ci * MAX_TPS + j],
+                                              z = (int32_t)tab_z[ci * MAX_TPS + j];
+                                if (CTAS == 2) tma_load_3d_pair(sb + j * box_bytes, &mapB, full, x, y, z);
+                                else tma_load_3d(sb + j * box_bytes, &mapB, full, x, y, z);
+                            }
                         } else {
 #pragma unroll
-                            for (int a = 0; a < A_ATOMS; ++a)
-                                tma_load_2d(sa + a * ATOM, &mapA, full, (int32_t)(tr * TILE_R + a * EPR), (int32_t)d0);
+                            for (int a = 0; a < A_ATOMS; ++a) {
+                                if (CTAS == 2) tma_load_2d_pair(sa + a * ATOM, &mapA, full, (int32_t)(row0 + a * EPR), (int32_t)d0);
+                                else tma_load_2d(sa + a * ATOM, &mapA, full, (int32_t)(row0 + a * EPR), (int32_t)d0);
+                            }
 #pragma unroll
-                            for (int j = 0; j < B_ATOMS; ++j)
-                                tma_load_2d(sb + j * ATOM, &mapB, full, (int32_t)(tc * TILE_C + j * EPR), (int32_t)d0);
+                            for (int j = 0; j < B_ATOMS; ++j) {
+                                if (CTAS == 2) tma_load_2d_pair(sb + j * ATOM, &mapB, full, (int32_t)(col0 + j * EPR), (int32_t)d0);
+                                else tma_load_2d(sb + j * ATOM, &mapB, full, (int32_t)(col0 + j * EPR), (int32_t)d0);
+                            }
                         }
                     }
                     if (ok) it += nb;
@@ -215,15 +263,15 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 it = __shfl_sync(0xffffffffu, it, 0);
             }
         }
-        if (!ok && lane == 0) {
+        if (!ok && lane == 0 && rank == 0) {
             // give the loads already issued time to land before the CTA retires
             const uint32_t lo = it > STAGES ? it - STAGES : 0;
             for (uint32_t g = lo; g < it; ++g) wait_cycles(bar_full + 8 * (g % STAGES), (g / STAGES) & 1, 4000000);
         }
     } else if (warp == 1) {
-        // ===================== MMA issuer =====================
+        // ===================== MMA issuer (leader CTA only) =====================
         uint32_t it = 0, n_items = 0;
-        for (uint32_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x, ++n_items) {
+        for (uint32_t item = first_item; item < p.total_items && ok && rank == 0; item += item_stride, ++n_items) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
             const uint32_t buf = n_items & 1, tph = (n_items >> 1) & 1;
@@ -243,27 +291,37 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     for (int kk = 0; kk < MMAS; ++kk) {
                         const uint64_t ad = make_desc_sw128(sa + kk * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
                         const uint64_t bd = make_desc_sw128(sb + kk * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
-                        tc_mma<TF32>(d_tmem, ad, bd, p.idesc, (c > c_begin || kk > 0) ? 1u : 0u);
+                        const uint32_t acc = (c > c_begin || kk > 0) ? 1u : 0u;
+                        if (CTAS == 2) tc_mma_pair<TF32>(d_tmem, ad, bd, p.idesc, acc);
+                        else tc_mma<TF32>(d_tmem, ad, bd, p.idesc, acc);
                     }
-                    tc_commit(bar_empty + 8 * s);
+                    // frees this stage in both CTAs once the MMAs have read it
+                    if (CTAS == 2) tc_commit_pair(bar_empty + 8 * s, 3);
+                    else tc_commit(bar_empty + 8 * s);
                 }
-                if (ok) tc_commit(bar_tfull + 8 * buf);
+                if (ok) {
+                    if (CTAS == 2) tc_commit_pair(bar_tfull + 8 * buf, 3);
+                    else tc_commit(bar_tfull + 8 * buf);
+                }
             }
             __syncwarp();
             ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             it = __shfl_sync(0xffffffffu, it, 0);
         }
-        if (!ok && lane == 0) {
+        if (!ok && lane == 0 && rank == 0) {
             // MMAs may still be running: wait (bounded) until the tensor core has drained
-            tc_commit(bar_drain);
+            if (CTAS == 2) tc_commit_pair(bar_drain, 1);
+            else tc_commit(bar_drain);
             wait_cycles(bar_drain, 0, 20000000);
         }
     } else {
-        // ===================== epilogue =====================
+        // ===================== epilogue (both CTAs; each drains its own 128 rows) =====================
         const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
         float *scratch = epi_scratch + q * (32 * 33);
+        uint32_t tempty_base = bar_tempty;
+        if (CTAS == 2) tempty_base = mapa_cluster(bar_tempty, 0);
         uint32_t n_items = 0;
-        for (uint32_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x, ++n_items) {
+        for (uint32_t item = first_item; item < p.total_items && ok; item += item_stride, ++n_items) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
             const uint32_t buf = n_items & 1, tph = (n_items >> 1) & 1;
@@ -271,7 +329,8 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             ok = __all_sync(0xffffffffu, mine);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t row = tr * TILE_R + q * 32 + lane;
+            const uint32_t rbase = tr * PAIR_R + rank * TILE_R + q * 32;   // first row of this warp
+            const uint32_t row = rbase + lane;
 #pragma unroll 1
             for (int c = 0; c < TILE_C / 32; ++c) {
                 uint32_t v[32];
@@ -282,7 +341,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
 #pragma unroll
                     for (int j = 0; j < 32; ++j) scratch[lane * 33 + j] = __uint_as_float(v[j]) * p.alpha;
                     __syncwarp();
-                    const uint32_t kb = tr * TILE_R + q * 32;
+                    const uint32_t kb = rbase;
                     if (kb < p.K && col < p.N) {
                         const uint32_t pk = kb / (uint32_t)p.hash.BK, pn = col / (uint32_t)p.hash.BN;
                         float *dst = p.dH + rz_tile_offset(p.hash, pk, pn) +
@@ -336,16 +395,21 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+            if (lane == 0) {
+                if (CTAS == 2) mbar_arrive_cluster(tempty_base + 8 * buf);
+                else mbar_arrive(bar_tempty + 8 * buf);
+            }
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    if (CTAS == 2) cluster_sync_all();   // neither CTA retires while the peer may still signal or read it
     if (warp == 1) {
         tc_fence_after();
         __syncwarp();
-        tmem_dealloc(tmem_base, 512);
+        if (CTAS == 2) tmem_dealloc_pair(tmem_base, 512);
+        else tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -495,13 +559,33 @@ uint32_t env_u32(const char *name, uint32_t dflt)
     return s ? (uint32_t)strtoul(s, nullptr, 0) : dflt;
 }
 
-template <int OP, bool TF32>
+// How many CTAs cooperate on one output block: 2 (a cluster pair driving cta_group::2 MMAs) unless the
+// problem is too small to give every pair work, or RZ_TC_CTAS overrides it.
+int choose_ctas(const rz_problem *pb, int op)
+{
+    const uint32_t forced = env_u32("RZ_TC_CTAS", 0);
+    if (forced == 1 || forced == 2) return (int)forced;
+    const int64_t rows = (op == RZ_OP_BACKWARD_WEIGHT) ? pb->K : pb->M;
+    return rows >= 2 * TILE_R ? 2 : 1;
+}
+
+uint32_t dx_box_rows(const rz_problem *pb, int ctas)
+{
+    const uint32_t bcols = (uint32_t)(TILE_C / ctas);
+    uint32_t br = (uint32_t)pb->BK < bcols ? (uint32_t)pb->BK : bcols;
+    const uint32_t forced = env_u32("RZ_TC_BR", 0);
+    if (forced && forced <= br && br % forced == 0 && TILE_C / ctas / forced <= MAX_TPS) br = forced;
+    return br;
+}
+
+template <int OP, bool TF32, int CTAS>
 int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p)
 {
     const rz_problem *pb = c.pb;
     constexpr int ES = TF32 ? 4 : 2;
     constexpr int EPR = 128 / ES;
     constexpr int KC = EPR;
+    constexpr int PAIR_R = TILE_R * CTAS;
     p.hash = c.hash;
     p.M = (uint32_t)pb->M;
     p.K = (uint32_t)pb->K;
@@ -509,15 +593,48 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.rows = (OP == OP_DW) ? p.K : p.M;
     p.cols = (OP == OP_DX) ? p.K : p.N;
     const uint32_t depth = (OP == OP_FWD) ? p.K : (OP == OP_DX ? p.N : p.M);
-    p.tiles_r = (p.rows + TILE_R - 1) / TILE_R;
+    p.tiles_r = (p.rows + PAIR_R - 1) / PAIR_R;
     p.tiles_c = (p.cols + TILE_C - 1) / TILE_C;
     p.nchunks = (depth + KC - 1) / KC;
-    const int sms = num_sms();
+    p.br = dx_box_rows(pb, CTAS);
+    p.group_rows = env_u32("RZ_TC_GROUP", GROUP_ROWS);
+    if (p.group_rows < 1) p.group_rows = 1;
+
+    auto kern = rz_tc_kernel<OP, TF32, CTAS>;
+    constexpr int SMEM_TOTAL = smem_total(OP, CTAS);
+    static_assert(SMEM_TOTAL <= SMEM_LIMIT, "shared memory budget");
+    int st = rz_record_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL),
+                            "set max dynamic shared memory");
+    if (st) return st;
+
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    cfg.blockDim = dim3(NTHREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_TOTAL;
+    cfg.stream = c.stream;
+    cfg.numAttrs = 0;
+    // number of blocks (CTAS = 1) or CTA pairs (CTAS = 2) that can be resident at once
+    int slots = num_sms() / CTAS;
+    if (CTAS == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cfg.gridDim = dim3(2 * (unsigned)slots, 1, 1);
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) == cudaSuccess && clusters > 0 && clusters < slots)
+            slots = clusters;
+        (void)cudaGetLastError();
+    }
+
     const uint32_t tiles = p.tiles_r * p.tiles_c;
     p.nsplit = 1;
-    if (OP == OP_DW && tiles < (uint32_t)sms) {
+    if (OP == OP_DW && tiles < (uint32_t)slots) {
         // split the batch so that every SM gets work; each split adds into dH independently
-        uint32_t want = ((uint32_t)sms + tiles - 1) / tiles;
+        uint32_t want = ((uint32_t)slots + tiles - 1) / tiles;
         uint32_t max_split = (p.nchunks + 7) / 8;  // at least 8 stages per split
         if (max_split < 1) max_split = 1;
         p.nsplit = want < max_split ? want : max_split;
@@ -552,25 +669,22 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     const uint32_t a_major = (OP == OP_DW) ? 1u : 0u, b_major = (OP == OP_DX) ? 0u : 1u;
     const uint32_t fmt = TF32 ? 2u : 1u;
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (a_major << 15) | (b_major << 16) | ((uint32_t)(TILE_C >> 3) << 17) |
-              ((uint32_t)(TILE_R >> 4) << 24);
+              ((uint32_t)(PAIR_R >> 4) << 24);
 
-    // bring-up overrides of the descriptor strides
-    p.a_lbo = env_u32("RZ_TC_A_LBO", p.a_lbo);
-    p.a_sbo = env_u32("RZ_TC_A_SBO", p.a_sbo);
-    p.a_kstep = env_u32("RZ_TC_A_KSTEP", p.a_kstep);
-    p.b_lbo = env_u32("RZ_TC_B_LBO", p.b_lbo);
-    p.b_sbo = env_u32("RZ_TC_B_SBO", p.b_sbo);
-    p.b_kstep = env_u32("RZ_TC_B_KSTEP", p.b_kstep);
-    p.idesc = env_u32("RZ_TC_IDESC", p.idesc);
-
-    auto kern = rz_tc_kernel<OP, TF32>;
-    int st = rz_record_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL),
-                            "set max dynamic shared memory");
-    if (st) return st;
-    const uint32_t grid = p.total_items < (uint32_t)sms ? p.total_items : (uint32_t)sms;
-    kern<<<grid, NTHREADS, SMEM_TOTAL, c.stream>>>(mapA, mapB, p);
+    const uint32_t blocks = p.total_items < (uint32_t)slots ? p.total_items : (uint32_t)slots;
+    cfg.gridDim = dim3(blocks * CTAS, 1, 1);
+    st = rz_record_cuda(cudaLaunchKernelEx(&cfg, kern, mapA, mapB, p), "tcgen05 kernel launch");
     rz_count_launch(1);
+    if (st) return st;
     return rz_record_cuda(cudaGetLastError(), "tcgen05 kernel launch");
+}
+
+template <int OP>
+int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, int ctas)
+{
+    const bool tf32 = c.pb->precision == RZ_PREC_TF32;
+    if (ctas == 2) return tf32 ? launch_tc<OP, true, 2>(c, mapA, mapB, p) : launch_tc<OP, false, 2>(c, mapA, mapB, p);
+    return tf32 ? launch_tc<OP, true, 1>(c, mapA, mapB, p) : launch_tc<OP, false, 1>(c, mapA, mapB, p);
 }
 
 // 2-D map over a row-major matrix [rows][cols] of the operand type
@@ -603,7 +717,7 @@ bool rz_tc_supported(const rz_problem *pb, int op)
     if (pb->precision != RZ_PREC_TF32 && pb->precision != RZ_PREC_BF16) return false;
     const Geometry g = geometry(pb);
     if (pb->BK % g.epr || pb->BN % g.epr) return false;
-    if (pb->BK <= 256 ? (256 % pb->BK != 0) : (pb->BK % 256 != 0)) return false;
+    if (pb->BK <= 128 ? (128 % pb->BK != 0) : (pb->BK % 128 != 0)) return false;  // whole B boxes per hash tile
     if ((pb->K * g.es) % 16 || (pb->N * g.es) % 16) return false;
     if (pb->M < TILE_R || pb->K < g.epr || pb->N < g.epr) return false;  // TMA boxes no larger than the matrices
     return true;
@@ -656,7 +770,7 @@ int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const
     memset(&p, 0, sizeof(p));
     p.bias = bias;
     p.out = Y;
-    return tf32 ? launch_tc<OP_FWD, true>(c, mapA, mapB, p) : launch_tc<OP_FWD, false>(c, mapA, mapB, p);
+    return launch_tc_any<OP_FWD>(c, mapA, mapB, p, choose_ctas(pb, RZ_OP_FORWARD));
 }
 
 int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shadow, void *dX)
@@ -667,14 +781,13 @@ int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shado
     CUtensorMap mapA, mapB;
     int st = map_matrix(&mapA, tf32, false, dY, pb->M, pb->N, g.epr, TILE_R);
     if (st) return st;
-    const uint32_t br = pb->BK < 256 ? (uint32_t)pb->BK : 256u;
-    st = map_shadow(&mapB, pb, false, shadow, br);
+    const int ctas = choose_ctas(pb, RZ_OP_BACKWARD_INPUT);
+    st = map_shadow(&mapB, pb, false, shadow, dx_box_rows(pb, ctas));
     if (st) return st;
     TcParams p;
     memset(&p, 0, sizeof(p));
-    p.br = br;
     p.out = dX;
-    return tf32 ? launch_tc<OP_DX, true>(c, mapA, mapB, p) : launch_tc<OP_DX, false>(c, mapA, mapB, p);
+    return launch_tc_any<OP_DX>(c, mapA, mapB, p, ctas);
 }
 
 int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, float *dH)
@@ -690,5 +803,5 @@ int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, f
     TcParams p;
     memset(&p, 0, sizeof(p));
     p.dH = dH;
-    return tf32 ? launch_tc<OP_DW, true>(c, mapA, mapB, p) : launch_tc<OP_DW, false>(c, mapA, mapB, p);
+    return launch_tc_any<OP_DW>(c, mapA, mapB, p, choose_ctas(pb, RZ_OP_BACKWARD_WEIGHT));
 }
