@@ -4,15 +4,19 @@
 //   OP_FWD  Y [M,N] = X  [M,K] . W[K,N]      A = X tile  (K-major),  B = W slice (N-major)
 //   OP_DX   dX[M,K] = dY [M,N] . W[K,N]^T    A = dY tile (K-major),  B = W slice (K-major)
 //   OP_DW   dH     += X^T[K,M] . dY[M,N]     A = X tile  (M-major),  B = dY tile (N-major)
-// CTAS = 1: a CTA owns a 128 x 256 output block (tcgen05.mma cta_group::1, M = 128).
-// CTAS = 2: two CTAs of a cluster own a 256 x 256 block (cta_group::2, M = 256): each CTA stages its
-//           128 rows of A and its 128 columns of B, so every SM pulls 32 KB instead of 48 KB from L2
-//           per pipeline stage, which is what bounds the 1-CTA kernel.  The leader CTA (rank 0)
-//           issues the MMAs for both; barriers that gate them live in the leader.
-// The accumulator lives in TMEM (two 256-column buffers, so the epilogue of one block overlaps the
-// main loop of the next).  Warp 0 produces (TMA loads into a ring of 128-byte-swizzled shared-memory
-// tiles), warp 1 issues tcgen05.mma, warps 2-5 drain TMEM: they scale/bias/convert and store (FWD, DX)
-// or scatter-add into the hashed gradient with warp-wide coalesced reductions (DW).
+// CTAS = 1, RB = 1: a CTA owns a 128 x 256 output block (tcgen05.mma cta_group::1, M = 128).
+// CTAS = 2, RB = 1: two CTAs of a cluster own a 256 x 256 block (cta_group::2, M = 256): each CTA
+//           stages its 128 rows of A and its 128 columns of B.  The leader CTA (rank 0) issues the
+//           MMAs for both; the barriers that gate them live in the leader.
+// CTAS = 2, RB = 2: the pair owns a 512 x 256 block as two M = 256 MMAs per K-step that share B: each CTA
+//           stages 2 x 128 rows of A and 128 columns of B, i.e. 48 KB per 1024 tensor-clocks instead of
+//           32 KB per 512.  The kernels are bound by what an SM can pull from L2 (about 50 B/clk), so
+//           this is the fast configuration; it is used whenever the output has at least 512 rows.
+// Accumulators live in TMEM (512 columns): with RB = 1 two 256-column buffers alternate so the epilogue of
+// one block overlaps the main loop of the next; with RB = 2 both halves are accumulators of one block.
+// Warp 0 produces (TMA loads into a ring of 128-byte-swizzled shared-memory tiles), warp 1 issues
+// tcgen05.mma, 4*RB epilogue warps drain TMEM: they scale/bias/convert and store (FWD, DX) or scatter-add
+// into the hashed gradient with warp-wide coalesced reductions (DW).
 //
 // The virtual weight is never materialised.  For every pipeline stage the producer warp computes
 // the hash-tile offsets in registers and TMA-loads the matching rows of the slice.  TMA needs a
@@ -38,32 +42,32 @@ namespace {
 
 constexpr int OP_FWD = 0, OP_DX = 1, OP_DW = 2;
 
-constexpr int TILE_R = 128;  // rows per CTA (MMA M = 128 * CTAS)
+constexpr int TILE_R = 128;  // rows per CTA and accumulator (MMA M = 128 * CTAS)
 constexpr int TILE_C = 256;  // MMA N
-constexpr int A_BYTES = 16384;
-constexpr int NTHREADS = 192;
+constexpr int A_BLOCK_BYTES = 16384;  // one 128-row block of A per stage
 constexpr int BATCH = 8;     // pipeline stages per hash batch of the producer warp
 constexpr int MAX_TPS = 8;   // B boxes per stage at most
-constexpr int GROUP_ROWS = 8;
+constexpr int GROUP_ROWS = 8;   // row tiles per rasterisation group (4 when a tile has two row blocks)
 
 // Shared-memory budget (227 KB per CTA): the operand ring takes what the other parts leave.
 // Only the weight-gradient epilogue needs transpose scratch, so FWD / DX get one more 32 KB stage.
-constexpr int SMEM_EPI = 4 * 32 * 33 * 4;
+constexpr int SMEM_EPI_WARP = 32 * 33 * 4;
 constexpr int SMEM_TABLE = 3 * BATCH * MAX_TPS * 4;
 constexpr int MAX_STAGES = 7;
 constexpr int SMEM_BARS = (2 * MAX_STAGES + 5) * 8;
 constexpr int SMEM_LIMIT = 232448;
-__host__ __device__ constexpr int smem_epi(int op) { return op == OP_DW ? SMEM_EPI : 0; }
-__host__ __device__ constexpr int stage_bytes(int ctas) { return A_BYTES + (TILE_C / ctas) * 128; }
-__host__ __device__ constexpr int num_stages(int op, int ctas)
+__host__ __device__ constexpr int smem_epi(int op, int rb) { return op == OP_DW ? 4 * rb * SMEM_EPI_WARP : 0; }
+__host__ __device__ constexpr int stage_bytes(int ctas, int rb) { return rb * A_BLOCK_BYTES + (TILE_C / ctas) * 128; }
+__host__ __device__ constexpr int num_stages(int op, int ctas, int rb)
 {
-    int n = (SMEM_LIMIT - 1024 - 16 - SMEM_BARS - SMEM_TABLE - smem_epi(op)) / stage_bytes(ctas);
+    int n = (SMEM_LIMIT - 1024 - 16 - SMEM_BARS - SMEM_TABLE - smem_epi(op, rb)) / stage_bytes(ctas, rb);
     return n > MAX_STAGES ? MAX_STAGES : n;
 }
-__host__ __device__ constexpr int smem_total(int op, int ctas)
+__host__ __device__ constexpr int smem_total(int op, int ctas, int rb)
 {
-    return num_stages(op, ctas) * stage_bytes(ctas) + smem_epi(op) + SMEM_TABLE + SMEM_BARS + 16 + 1024;
+    return num_stages(op, ctas, rb) * stage_bytes(ctas, rb) + smem_epi(op, rb) + SMEM_TABLE + SMEM_BARS + 16 + 1024;
 }
+__host__ __device__ constexpr int num_threads(int rb) { return 64 + 128 * rb; }
 
 struct TcParams {
     RzHash hash;
@@ -94,8 +98,8 @@ __device__ __forceinline__ void wait_cycles(uint32_t bar, uint32_t parity, long 
         if (clock64() - t0 > cycles) break;
 }
 
-template <int OP, bool TF32, int CTAS>
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <int OP, bool TF32, int CTAS, int RB>
+__global__ void __launch_bounds__(num_threads(RB), 1)
 rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
     constexpr int ES = TF32 ? 4 : 2;        // operand element size
@@ -106,14 +110,18 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     constexpr int ATOM = KC * 128;          // bytes of one 128-byte-wide column block of an MN-major tile
     constexpr int B_COLS = TILE_C / CTAS;   // columns of B this CTA stages
     constexpr int B_BYTES = B_COLS * 128;
+    constexpr int A_BYTES = RB * A_BLOCK_BYTES;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int STAGES = num_stages(OP, CTAS);
+    constexpr int STAGES = num_stages(OP, CTAS, RB);
     constexpr int SMEM_RING = STAGES * STAGE_BYTES;
-    constexpr int SMEM_EPI_OP = smem_epi(OP);
-    static_assert(STAGE_BYTES == stage_bytes(CTAS), "stage size");
+    constexpr int SMEM_EPI_OP = smem_epi(OP, RB);
+    constexpr int NBUF = 2 / RB;            // accumulator sets in TMEM (2: double-buffered, 1: none spare)
+    static_assert(STAGE_BYTES == stage_bytes(CTAS, RB), "stage size");
+    static_assert(RB == 1 || CTAS == 2, "two row blocks only with CTA pairs");
     constexpr int A_ATOMS = TILE_R / EPR;
     constexpr int B_ATOMS = B_COLS / EPR;
-    constexpr int PAIR_R = TILE_R * CTAS;   // rows of a work item
+    constexpr int PAIR_R = TILE_R * CTAS;   // rows of one accumulator across the pair
+    constexpr int ITEM_R = PAIR_R * RB;     // rows of a work item
     static_assert(STAGES <= MAX_STAGES, "barrier storage");
 
     extern __shared__ uint8_t smem_raw[];
@@ -143,7 +151,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_tfull + 8 * b, 1);
-            mbar_init(bar_tempty + 8 * b, 4 * CTAS);
+            mbar_init(bar_tempty + 8 * b, 4 * RB * CTAS);
         }
         mbar_init(bar_drain, 1);
         fence_barrier_init();
@@ -190,7 +198,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         for (uint32_t item = first_item; item < p.total_items && ok; item += item_stride) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
-            const uint32_t row0 = tr * PAIR_R + rank * TILE_R;     // first output row staged by this CTA (A)
+            const uint32_t row0 = tr * ITEM_R + rank * TILE_R;     // first output row staged by this CTA (A); row block r adds r * PAIR_R
             const uint32_t col0 = tc * TILE_C + rank * B_COLS;     // first output column staged by this CTA (B)
             for (uint32_t cb = c_begin; cb < c_end && ok; cb += BATCH) {
                 const uint32_t nb = min((uint32_t)BATCH, c_end - cb);
@@ -233,8 +241,13 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                         if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, STAGE_BYTES * CTAS);
                         const uint32_t d0 = (cb + ci) * KC;  // contraction start of this stage
                         if (OP == OP_FWD || OP == OP_DX) {
-                            if (CTAS == 2) tma_load_2d_pair(sa, &mapA, full, (int32_t)d0, (int32_t)row0);
-                            else tma_load_2d(sa, &mapA, full, (int32_t)d0, (int32_t)row0);
+#pragma unroll
+                            for (int r = 0; r < RB; ++r) {
+                                if (CTAS == 2)
+                                    tma_load_2d_pair(sa + r * A_BLOCK_BYTES, &mapA, full, (int32_t)d0, (int32_t)(row0 + r * PAIR_R));
+                                else
+                                    tma_load_2d(sa, &mapA, full, (int32_t)d0, (int32_t)row0);
+                            }
                             const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS : (uint32_t)B_COLS / p.br;
                             const uint32_t box_bytes = (OP == OP_FWD) ? (uint32_t)ATOM : p.br * 128u;
                             for (uint32_t j = 0; j < tps; ++j) {
@@ -245,9 +258,14 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                             }
                         } else {
 #pragma unroll
-                            for (int a = 0; a < A_ATOMS; ++a) {
-                                if (CTAS == 2) tma_load_2d_pair(sa + a * ATOM, &mapA, full, (int32_t)(row0 + a * EPR), (int32_t)d0);
-                                else tma_load_2d(sa + a * ATOM, &mapA, full, (int32_t)(row0 + a * EPR), (int32_t)d0);
+                            for (int r = 0; r < RB; ++r) {
+#pragma unroll
+                                for (int a = 0; a < A_ATOMS; ++a) {
+                                    const uint32_t dst = sa + r * A_BLOCK_BYTES + a * ATOM;
+                                    const int32_t x = (int32_t)(row0 + r * PAIR_R + a * EPR);
+                                    if (CTAS == 2) tma_load_2d_pair(dst, &mapA, full, x, (int32_t)d0);
+                                    else tma_load_2d(dst, &mapA, full, x, (int32_t)d0);
+                                }
                             }
 #pragma unroll
                             for (int j = 0; j < B_ATOMS; ++j) {
@@ -274,11 +292,11 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         for (uint32_t item = first_item; item < p.total_items && ok && rank == 0; item += item_stride, ++n_items) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
-            const uint32_t buf = n_items & 1, tph = (n_items >> 1) & 1;
+            const uint32_t buf = n_items % NBUF, tph = (n_items / NBUF) & 1;
             if (lane == 0) {
                 if (!mbar_wait_bounded(bar_tempty + 8 * buf, tph ^ 1, RZ_WAIT_TMEM_EMPTY, p.status, p.wait_limit)) ok = false;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * TILE_C;
+                const uint32_t d_tmem = tmem_base + buf * RB * TILE_C;
                 for (uint32_t c = c_begin; c < c_end && ok; ++c, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     if (!mbar_wait_bounded(bar_full + 8 * s, ph, RZ_WAIT_SMEM_FULL, p.status, p.wait_limit)) {
@@ -289,11 +307,15 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
 #pragma unroll
                     for (int kk = 0; kk < MMAS; ++kk) {
-                        const uint64_t ad = make_desc_sw128(sa + kk * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
                         const uint64_t bd = make_desc_sw128(sb + kk * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
                         const uint32_t acc = (c > c_begin || kk > 0) ? 1u : 0u;
-                        if (CTAS == 2) tc_mma_pair<TF32>(d_tmem, ad, bd, p.idesc, acc);
-                        else tc_mma<TF32>(d_tmem, ad, bd, p.idesc, acc);
+#pragma unroll
+                        for (int r = 0; r < RB; ++r) {
+                            const uint64_t ad =
+                                make_desc_sw128(sa + r * A_BLOCK_BYTES + kk * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
+                            if (CTAS == 2) tc_mma_pair<TF32>(d_tmem + r * TILE_C, ad, bd, p.idesc, acc);
+                            else tc_mma<TF32>(d_tmem, ad, bd, p.idesc, acc);
+                        }
                     }
                     // frees this stage in both CTAs once the MMAs have read it
                     if (CTAS == 2) tc_commit_pair(bar_empty + 8 * s, 3);
@@ -316,25 +338,26 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         }
     } else {
         // ===================== epilogue (both CTAs; each drains its own 128 rows) =====================
-        const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
-        float *scratch = epi_scratch + q * (32 * 33);
+        const uint32_t q = warp & 3;          // TMEM lane quarter this warp may read
+        const uint32_t rblk = (warp - 2) >> 2;  // which accumulator (row block) of the item this warp drains
+        float *scratch = epi_scratch + (warp - 2) * (32 * 33);
         uint32_t tempty_base = bar_tempty;
         if (CTAS == 2) tempty_base = mapa_cluster(bar_tempty, 0);
         uint32_t n_items = 0;
         for (uint32_t item = first_item; item < p.total_items && ok; item += item_stride, ++n_items) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
-            const uint32_t buf = n_items & 1, tph = (n_items >> 1) & 1;
+            const uint32_t buf = n_items % NBUF, tph = (n_items / NBUF) & 1;
             bool mine = mbar_wait_bounded(bar_tfull + 8 * buf, tph, RZ_WAIT_TMEM_FULL, p.status, p.wait_limit);
             ok = __all_sync(0xffffffffu, mine);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t rbase = tr * PAIR_R + rank * TILE_R + q * 32;   // first row of this warp
+            const uint32_t rbase = tr * ITEM_R + rblk * PAIR_R + rank * TILE_R + q * 32;   // first row of this warp
             const uint32_t row = rbase + lane;
 #pragma unroll 1
             for (int c = 0; c < TILE_C / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + buf * TILE_C + c * 32, v);
+                tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + (buf * RB + rblk) * TILE_C + c * 32, v);
                 tmem_ld_wait();
                 const uint32_t col = tc * TILE_C + c * 32;
                 if (OP == OP_DW) {
@@ -559,15 +582,18 @@ uint32_t env_u32(const char *name, uint32_t dflt)
     return s ? (uint32_t)strtoul(s, nullptr, 0) : dflt;
 }
 
-// How many CTAs cooperate on one output block: 2 (a cluster pair driving cta_group::2 MMAs) unless the
-// problem is too small to give every pair work, or RZ_TC_CTAS overrides it.
-int choose_ctas(const rz_problem *pb, int op)
+// Kernel configuration: 1 = one CTA per 128x256 block, 2 = CTA pair per 256x256 block, 3 = CTA pair per
+// 512x256 block (two row blocks sharing B).  The largest block the output's row count fills is used;
+// RZ_TC_CONFIG overrides it.
+int choose_config(const rz_problem *pb, int op)
 {
-    const uint32_t forced = env_u32("RZ_TC_CTAS", 0);
-    if (forced == 1 || forced == 2) return (int)forced;
+    const uint32_t forced = env_u32("RZ_TC_CONFIG", 0);
+    if (forced >= 1 && forced <= 3) return (int)forced;
     const int64_t rows = (op == RZ_OP_BACKWARD_WEIGHT) ? pb->K : pb->M;
+    if (rows >= 4 * TILE_R) return 3;
     return rows >= 2 * TILE_R ? 2 : 1;
 }
+int config_ctas(int config) { return config == 1 ? 1 : 2; }
 
 uint32_t dx_box_rows(const rz_problem *pb, int ctas)
 {
@@ -578,7 +604,7 @@ uint32_t dx_box_rows(const rz_problem *pb, int ctas)
     return br;
 }
 
-template <int OP, bool TF32, int CTAS>
+template <int OP, bool TF32, int CTAS, int RB>
 int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p)
 {
     const rz_problem *pb = c.pb;
@@ -586,6 +612,8 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     constexpr int EPR = 128 / ES;
     constexpr int KC = EPR;
     constexpr int PAIR_R = TILE_R * CTAS;
+    constexpr int ITEM_R = PAIR_R * RB;
+    constexpr int NTHREADS = num_threads(RB);
     p.hash = c.hash;
     p.M = (uint32_t)pb->M;
     p.K = (uint32_t)pb->K;
@@ -593,15 +621,15 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.rows = (OP == OP_DW) ? p.K : p.M;
     p.cols = (OP == OP_DX) ? p.K : p.N;
     const uint32_t depth = (OP == OP_FWD) ? p.K : (OP == OP_DX ? p.N : p.M);
-    p.tiles_r = (p.rows + PAIR_R - 1) / PAIR_R;
+    p.tiles_r = (p.rows + ITEM_R - 1) / ITEM_R;
     p.tiles_c = (p.cols + TILE_C - 1) / TILE_C;
     p.nchunks = (depth + KC - 1) / KC;
     p.br = dx_box_rows(pb, CTAS);
-    p.group_rows = env_u32("RZ_TC_GROUP", GROUP_ROWS);
+    p.group_rows = env_u32("RZ_TC_GROUP", GROUP_ROWS / RB);
     if (p.group_rows < 1) p.group_rows = 1;
 
-    auto kern = rz_tc_kernel<OP, TF32, CTAS>;
-    constexpr int SMEM_TOTAL = smem_total(OP, CTAS);
+    auto kern = rz_tc_kernel<OP, TF32, CTAS, RB>;
+    constexpr int SMEM_TOTAL = smem_total(OP, CTAS, RB);
     static_assert(SMEM_TOTAL <= SMEM_LIMIT, "shared memory budget");
     int st = rz_record_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL),
                             "set max dynamic shared memory");
@@ -680,11 +708,14 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
 }
 
 template <int OP>
-int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, int ctas)
+int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, int config)
 {
     const bool tf32 = c.pb->precision == RZ_PREC_TF32;
-    if (ctas == 2) return tf32 ? launch_tc<OP, true, 2>(c, mapA, mapB, p) : launch_tc<OP, false, 2>(c, mapA, mapB, p);
-    return tf32 ? launch_tc<OP, true, 1>(c, mapA, mapB, p) : launch_tc<OP, false, 1>(c, mapA, mapB, p);
+    if (config == 3)
+        return tf32 ? launch_tc<OP, true, 2, 2>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 2>(c, mapA, mapB, p);
+    if (config == 2)
+        return tf32 ? launch_tc<OP, true, 2, 1>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 1>(c, mapA, mapB, p);
+    return tf32 ? launch_tc<OP, true, 1, 1>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1>(c, mapA, mapB, p);
 }
 
 // 2-D map over a row-major matrix [rows][cols] of the operand type
@@ -770,7 +801,7 @@ int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const
     memset(&p, 0, sizeof(p));
     p.bias = bias;
     p.out = Y;
-    return launch_tc_any<OP_FWD>(c, mapA, mapB, p, choose_ctas(pb, RZ_OP_FORWARD));
+    return launch_tc_any<OP_FWD>(c, mapA, mapB, p, choose_config(pb, RZ_OP_FORWARD));
 }
 
 int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shadow, void *dX)
@@ -781,13 +812,13 @@ int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shado
     CUtensorMap mapA, mapB;
     int st = map_matrix(&mapA, tf32, false, dY, pb->M, pb->N, g.epr, TILE_R);
     if (st) return st;
-    const int ctas = choose_ctas(pb, RZ_OP_BACKWARD_INPUT);
-    st = map_shadow(&mapB, pb, false, shadow, dx_box_rows(pb, ctas));
+    const int config = choose_config(pb, RZ_OP_BACKWARD_INPUT);
+    st = map_shadow(&mapB, pb, false, shadow, dx_box_rows(pb, config_ctas(config)));
     if (st) return st;
     TcParams p;
     memset(&p, 0, sizeof(p));
     p.out = dX;
-    return launch_tc_any<OP_DX>(c, mapA, mapB, p, ctas);
+    return launch_tc_any<OP_DX>(c, mapA, mapB, p, config);
 }
 
 int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, float *dH)
@@ -803,5 +834,5 @@ int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, f
     TcParams p;
     memset(&p, 0, sizeof(p));
     p.dH = dH;
-    return launch_tc_any<OP_DW>(c, mapA, mapB, p, choose_ctas(pb, RZ_OP_BACKWARD_WEIGHT));
+    return launch_tc_any<OP_DW>(c, mapA, mapB, p, choose_config(pb, RZ_OP_BACKWARD_WEIGHT));
 }
