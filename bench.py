@@ -44,6 +44,12 @@ def seeded_R(seed=1005):
     return [PRIME] + [int(v) for v in rs.randint(1, 2**31 - 1, 3)] + [0, 0, 0, 0]
 
 
+# DRAM bytes (read + write) per row of the shard moved by one launch of each tensor-core kernel, from the ncu
+# capture of the 8192-row case of this workload (dram__bytes_read.sum + dram__bytes_write.sum; the traffic
+# grows in proportion to the rows): forward 765 MB, weight gradient 1065 MB, input gradient 812 MB.
+DRAM_BYTES_PER_ROW = {"forward": 764.7e6 / 8192, "backward_weight": 1065.2e6 / 8192, "backward_input": 811.6e6 / 8192}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -316,7 +322,8 @@ def main():
         achieved = flops_kernel / (per_kernel[dom] * 1e-3) / 1e12
         peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
         roofline = {"bound": "tensor", "kernel": f"rz_tc_kernel<{dom}>", "achieved": achieved, "peak": peak,
-                    "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                    "unit": "TFLOP/s", "frac": achieved / peak, "traffic": DRAM_BYTES_PER_ROW[dom] * M,
+                    "traffic_source": "ncu dram bytes of the 8192-row case scaled by rows",
                     "peak_source": f"{peak_kind} bf16_tflops_sustained (kernel timed inside a long step)",
                     "ms_per_launch": per_kernel[dom]}
         line = {

@@ -71,7 +71,7 @@ class RzDataParallelStep:
         self.dH = torch.empty(H, dtype=torch.float32, device=self.device)
         self.Y = torch.empty((M_local, N), dtype=dtype, device=self.device)
         self.dX = torch.empty((M_local, K), dtype=dtype, device=self.device)
-        self._x_dev = self._dy_dev = None
+        self._pipe = None
 
     def load_weights(self, hashed: torch.Tensor) -> None:
         self.hashed.copy_(hashed.to(self.hashed.dtype), non_blocking=True)
@@ -98,13 +98,65 @@ class RzDataParallelStep:
         k.sgd(self.hashed, self.dH, self.lr)
         mark("sgd")
 
-    def step_host(self, X_host: torch.Tensor, dY_host: torch.Tensor, hashed_out_host: torch.Tensor) -> None:
-        """The same step fed from (pinned) host memory: copies the shards in, runs, copies the updated
-        hashed array back to `hashed_out_host`.  Asynchronous on the current stream."""
-        if self._x_dev is None:
-            self._x_dev = torch.empty((self.M, self.K), dtype=self.dtype, device=self.device)
-            self._dy_dev = torch.empty((self.M, self.N), dtype=self.dtype, device=self.device)
-        self._x_dev.copy_(X_host, non_blocking=True)
-        self._dy_dev.copy_(dY_host, non_blocking=True)
-        self.step(self._x_dev, self._dy_dev)
+    def _host_pipeline(self, chunk_rows: int):
+        """Device staging buffers, the copy stream, per-chunk problems and events of step_host."""
+        if getattr(self, "_pipe", None) is not None and self._pipe["chunk_rows"] == chunk_rows:
+            return self._pipe
+        spans = [(lo, min(self.M, lo + chunk_rows)) for lo in range(0, self.M, chunk_rows)]
+        base = self.pb
+        problems = []
+        for i, (lo, hi) in enumerate(spans):
+            flags = base.flags | (_lib.FLAG_ACCUMULATE_DH if i > 0 else 0)
+            pb = _lib.make_problem(hi - lo, self.K, self.N, self.H, base.BK, base.BN, list(base.R), base.hash_mode,
+                                   base.io_dtype, base.precision, base.alpha, flags)
+            problems.append(pb)
+        self._pipe = {
+            "chunk_rows": chunk_rows, "spans": spans, "problems": problems,
+            "x": torch.empty((self.M, self.K), dtype=self.dtype, device=self.device),
+            "dy": torch.empty((self.M, self.N), dtype=self.dtype, device=self.device),
+            "stream": torch.cuda.Stream(device=self.device),
+            "loaded": [torch.cuda.Event() for _ in spans],
+            "consumed": [None for _ in spans],
+        }
+        return self._pipe
+
+    def step_host(self, X_host: torch.Tensor, dY_host: torch.Tensor, hashed_out_host: torch.Tensor,
+                  chunk_rows: int = 16384) -> None:
+        """The same step fed from (pinned) host memory, asynchronous on the current stream.
+
+        The shards are copied in row chunks on a side stream while the kernels work on the chunks that
+        have already arrived (forward and input gradient are row-independent, the hashed-weight
+        gradient accumulates over chunks); the updated hashed array is copied back to
+        `hashed_out_host` at the end."""
+        if not isinstance(self.kernels, CudaKernels):
+            raise RuntimeError("step_host drives the CUDA kernels; use step() with injected kernels")
+        pipe = self._host_pipeline(min(chunk_rows, self.M))
+        main = torch.cuda.current_stream(self.device)
+        side = pipe["stream"]
+        shadow = self.kernels.shadow
+        side.wait_stream(main)   # inputs pinned/filled by work queued on the main stream so far
+        for i, (lo, hi) in enumerate(pipe["spans"]):
+            if pipe["consumed"][i] is not None:
+                side.wait_event(pipe["consumed"][i])   # the previous step has finished reading this chunk
+            with torch.cuda.stream(side):
+                pipe["x"][lo:hi].copy_(X_host[lo:hi], non_blocking=True)
+                pipe["dy"][lo:hi].copy_(dY_host[lo:hi], non_blocking=True)
+                pipe["loaded"][i].record(side)
+        work = None
+        last = len(pipe["spans"]) - 1
+        for i, (lo, hi) in enumerate(pipe["spans"]):
+            pb = pipe["problems"][i]
+            x, dy = pipe["x"][lo:hi], pipe["dy"][lo:hi]
+            main.wait_event(pipe["loaded"][i])
+            _lib.forward(pb, x, self.hashed, shadow, None, self.Y[lo:hi])
+            _lib.backward_weight(pb, x, dy, self.dH)
+            if i == last and self.world > 1:
+                work = dist.all_reduce(self.dH, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            _lib.backward_input(pb, dy, self.hashed, shadow, self.dX[lo:hi])
+            ev = torch.cuda.Event()
+            ev.record(main)
+            pipe["consumed"][i] = ev
+        if work is not None:
+            work.wait()
+        self.kernels.sgd(self.hashed, self.dH, self.lr)
         hashed_out_host.copy_(self.hashed, non_blocking=True)
