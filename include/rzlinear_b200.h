@@ -143,6 +143,12 @@ int rz_sgd_step(const rz_problem *pb, float *hashed, const float *dH, float lr, 
    RZ_ERR_PIPELINE; *detail (may be NULL) receives the code of the wait that gave up. */
 int rz_device_status(int *out, int *detail);
 
+/* Failure-detection self-test (no counterpart in the reference): launches a one-thread kernel that waits
+   on a barrier nothing completes, with the same bounded wait the tensor-core pipelines use.  After at
+   most `limit_cycles` SM cycles (1 .. 2e9) the wait gives up and the kernel returns; rz_device_status()
+   then reports RZ_ERR_PIPELINE with detail 6, and the context stays usable. */
+int rz_selftest_bounded_wait(int64_t limit_cycles, void *stream);
+
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t rz_launch_count(void);
 

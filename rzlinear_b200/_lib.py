@@ -28,6 +28,7 @@ EXPORTS = [
     "rz_hash_indices_device", "rz_plan", "rz_shadow_bytes", "rz_shadow_refresh",
     "rz_linear_forward", "rz_linear_backward_input", "rz_linear_backward_weight",
     "rz_linear_materialize", "rz_sgd_step", "rz_device_status", "rz_launch_count",
+    "rz_selftest_bounded_wait",
 ]
 
 
@@ -211,6 +212,16 @@ def device_status():
     st, detail = ctypes.c_int(0), ctypes.c_int(0)
     check(load().rz_device_status(ctypes.byref(st), ctypes.byref(detail)))
     return st.value, detail.value
+
+
+def selftest_bounded_wait(limit_cycles: int, device="cuda") -> None:
+    """Launch the bounded-wait self-test kernel; read the outcome with device_status()."""
+    fn = load().rz_selftest_bounded_wait
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int64, ctypes.c_void_p]
+    dev = torch.device(device)
+    with torch.cuda.device(dev):
+        check(fn(int(limit_cycles), _stream(dev)))
 
 
 def launch_count() -> int:

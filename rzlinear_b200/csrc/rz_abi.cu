@@ -243,6 +243,12 @@ int rz_device_status(int *out, int *detail)
     return RZ_OK;
 }
 
+int rz_selftest_bounded_wait(int64_t limit_cycles, void *stream)
+{
+    if (limit_cycles <= 0 || limit_cycles > 2000000000ll) return RZ_ERR_SHAPE;
+    return rz_tc_wait_selftest((long long)limit_cycles, reinterpret_cast<cudaStream_t>(stream));
+}
+
 uint64_t rz_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

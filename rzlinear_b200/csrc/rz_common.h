@@ -14,7 +14,8 @@ enum RzWaitCode {
     RZ_WAIT_SMEM_EMPTY = 2,
     RZ_WAIT_TMEM_FULL = 3,
     RZ_WAIT_TMEM_EMPTY = 4,
-    RZ_WAIT_STORE = 5
+    RZ_WAIT_STORE = 5,
+    RZ_WAIT_SELFTEST = 6
 };
 
 struct RzLaunchCtx {
@@ -43,3 +44,4 @@ int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float l
 int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const float *bias, void *Y);
 int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shadow, void *dX);
 int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, float *dH);
+int rz_tc_wait_selftest(long long limit_cycles, cudaStream_t stream);

@@ -56,7 +56,8 @@ constexpr int SMEM_TABLE = 3 * BATCH * MAX_TPS * 4;
 constexpr int MAX_STAGES = 7;
 constexpr int SMEM_BARS = (2 * MAX_STAGES + 5) * 8;
 constexpr int SMEM_LIMIT = 232448;
-__host__ __device__ constexpr int smem_epi(int op, int rb) { return op == OP_DW ? 4 * rb * SMEM_EPI_WARP : 0; }
+// per epilogue warp: a 32x33 fp32 transpose tile (DW) or a 32-row x 128-byte store staging tile (FWD, DX)
+__host__ __device__ constexpr int smem_epi(int op, int rb) { return 4 * rb * (op == OP_DW ? SMEM_EPI_WARP : 4096); }
 __host__ __device__ constexpr int stage_bytes(int ctas, int rb) { return rb * A_BLOCK_BYTES + (TILE_C / ctas) * 128; }
 __host__ __device__ constexpr int num_stages(int op, int ctas, int rb)
 {
@@ -340,7 +341,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         // ===================== epilogue (both CTAs; each drains its own 128 rows) =====================
         const uint32_t q = warp & 3;          // TMEM lane quarter this warp may read
         const uint32_t rblk = (warp - 2) >> 2;  // which accumulator (row block) of the item this warp drains
-        float *scratch = epi_scratch + (warp - 2) * (32 * 33);
+        float *scratch = epi_scratch + (warp - 2) * (OP == OP_DW ? 32 * 33 : 1024);
         uint32_t tempty_base = bar_tempty;
         if (CTAS == 2) tempty_base = mapa_cluster(bar_tempty, 0);
         uint32_t n_items = 0;
@@ -353,7 +354,6 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             if (!ok) break;
             tc_fence_after();
             const uint32_t rbase = tr * ITEM_R + rblk * PAIR_R + rank * TILE_R + q * 32;   // first row of this warp
-            const uint32_t row = rbase + lane;
 #pragma unroll 1
             for (int c = 0; c < TILE_C / 32; ++c) {
                 uint32_t v[32];
@@ -376,7 +376,10 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                             if (col_ok) atomicAdd(dst + (size_t)rr * (uint32_t)p.hash.BN, scratch[rr * 33 + lane]);
                     }
                     __syncwarp();
-                } else if (row < p.rows && col < p.cols) {
+                } else {
+                    // scale (+ bias, ReLU), convert, and stage this lane's row segment in shared memory in
+                    // 16-byte chunks (chunk index XOR row keeps both phases bank-conflict free); once a
+                    // 128-byte row segment is complete the warp writes it out 4 full rows per instruction.
                     float f[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
@@ -391,28 +394,44 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                             for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
                         }
                     }
-                    if (TF32) {
-                        float4 *o = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + (size_t)row * p.cols + col);
+                    uint8_t *stage = reinterpret_cast<uint8_t *>(scratch);
+                    constexpr int CHUNKS_PER_LD = TF32 ? 8 : 4;          // 16-byte chunks produced per 32 columns
+                    const int cbase = TF32 ? 0 : (c & 1) * 4;             // bf16: two loads fill one 128-byte row
 #pragma unroll
-                        for (int g = 0; g < 8; ++g)
-                            if (col + g * 4 < p.cols) o[g] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
-                    } else {
-                        uint4 *o = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + (size_t)row * p.cols + col);
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            if (col + g * 8 < p.cols) {
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(f[8 * g + 0], f[8 * g + 1]);
-                                __nv_bfloat162 h1 = __floats2bfloat162_rn(f[8 * g + 2], f[8 * g + 3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(f[8 * g + 4], f[8 * g + 5]);
-                                __nv_bfloat162 h3 = __floats2bfloat162_rn(f[8 * g + 6], f[8 * g + 7]);
-                                uint4 u;
-                                u.x = *reinterpret_cast<uint32_t *>(&h0);
-                                u.y = *reinterpret_cast<uint32_t *>(&h1);
-                                u.z = *reinterpret_cast<uint32_t *>(&h2);
-                                u.w = *reinterpret_cast<uint32_t *>(&h3);
-                                o[g] = u;
-                            }
+                    for (int g = 0; g < CHUNKS_PER_LD; ++g) {
+                        uint4 u;
+                        if (TF32) {
+                            u.x = __float_as_uint(f[4 * g + 0]);
+                            u.y = __float_as_uint(f[4 * g + 1]);
+                            u.z = __float_as_uint(f[4 * g + 2]);
+                            u.w = __float_as_uint(f[4 * g + 3]);
+                        } else {
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(f[8 * g + 0], f[8 * g + 1]);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(f[8 * g + 2], f[8 * g + 3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(f[8 * g + 4], f[8 * g + 5]);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(f[8 * g + 6], f[8 * g + 7]);
+                            u.x = *reinterpret_cast<uint32_t *>(&h0);
+                            u.y = *reinterpret_cast<uint32_t *>(&h1);
+                            u.z = *reinterpret_cast<uint32_t *>(&h2);
+                            u.w = *reinterpret_cast<uint32_t *>(&h3);
                         }
+                        *reinterpret_cast<uint4 *>(stage + lane * 128 + (((cbase + g) ^ (lane & 7)) * 16)) = u;
+                    }
+                    if (TF32 || (c & 1)) {
+                        __syncwarp();
+                        constexpr int EPC = TF32 ? 4 : 8;                 // elements per 16-byte chunk
+                        const uint32_t col_seg = TF32 ? col : col - 32;   // first column of the staged 128-byte segment
+                        const uint32_t cc = lane & 7, ccol = col_seg + cc * EPC;
+#pragma unroll
+                        for (int it4 = 0; it4 < 8; ++it4) {
+                            const uint32_t rr = it4 * 4 + (lane >> 3);
+                            const uint4 u = *reinterpret_cast<const uint4 *>(stage + rr * 128 + ((cc ^ (rr & 7)) * 16));
+                            const uint32_t grow = rbase + rr;
+                            if (grow < p.rows && ccol < p.cols)
+                                *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) +
+                                                           ((size_t)grow * p.cols + ccol) * (TF32 ? 4 : 2)) = u;
+                        }
+                        __syncwarp();
                     }
                 }
             }
@@ -433,6 +452,19 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         __syncwarp();
         if (CTAS == 2) tmem_dealloc_pair(tmem_base, 512);
         else tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- self-test of the bounded-wait machinery ---------------------------------------------------
+// One thread waits on an mbarrier that nothing will ever complete.  The wait must give up after
+// `limit` cycles, leave its code in the status word and let the kernel return normally.
+__global__ void rz_wait_selftest_kernel(int *status, long long limit)
+{
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        fence_barrier_init();
+        (void)mbar_wait_bounded(smem_u32(&bar), 0, RZ_WAIT_SELFTEST, status, limit);
     }
 }
 
@@ -590,7 +622,11 @@ int choose_config(const rz_problem *pb, int op)
     const uint32_t forced = env_u32("RZ_TC_CONFIG", 0);
     if (forced >= 1 && forced <= 3) return (int)forced;
     const int64_t rows = (op == RZ_OP_BACKWARD_WEIGHT) ? pb->K : pb->M;
-    if (rows >= 4 * TILE_R) return 3;
+    const int64_t depth = (op == RZ_OP_FORWARD) ? pb->K : (op == RZ_OP_BACKWARD_INPUT ? pb->N : pb->M);
+    const int64_t stages = depth / (pb->precision == RZ_PREC_TF32 ? 32 : 64);
+    // With two row blocks every TMEM column is an accumulator, so the epilogue cannot overlap the next
+    // block's main loop; that only pays off when the contraction is long enough to amortise it.
+    if (rows >= 4 * TILE_R && stages >= 24) return 3;
     return rows >= 2 * TILE_R ? 2 : 1;
 }
 int config_ctas(int config) { return config == 1 ? 1 : 2; }
@@ -741,6 +777,15 @@ int map_shadow(CUtensorMap *map, const rz_problem *pb, bool mn_major, const void
 }
 
 }  // namespace
+
+int rz_tc_wait_selftest(long long limit_cycles, cudaStream_t stream)
+{
+    int *status = rz_device_status_word();
+    if (!status) return rz_record_cuda(cudaErrorUnknown, "status word address");
+    rz_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, limit_cycles);
+    rz_count_launch(1);
+    return rz_record_cuda(cudaGetLastError(), "wait self-test launch");
+}
 
 bool rz_tc_supported(const rz_problem *pb, int op)
 {

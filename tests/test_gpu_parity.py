@@ -278,3 +278,20 @@ def test_tensor_core_two_level_hash_and_collisions(rzlib, L):
     assert o.rel_l2(Y, o.forward(X.float().numpy(), hf, N, BK, BN, R, 0)) < TOL_TC
     assert o.rel_l2(dH, o.backward_weight(X.float().numpy(), dY.float().numpy(), H, BK, BN, R, 0)) < TOL_TC
     check_status(rzlib)
+
+
+# ---------------------------------------------------------------------------------------------
+# failure detection: a device-side wait that runs out is reported, nothing hangs or faults
+# ---------------------------------------------------------------------------------------------
+def test_bounded_wait_reports_timeout_and_context_survives(rzlib, L):
+    assert rzlib.device_status() == (0, 0)
+    rzlib.selftest_bounded_wait(2_000_000, DEV)          # about a millisecond of waiting on a flag nothing sets
+    st, detail = rzlib.device_status()
+    assert st == -8 and detail == 6                      # RZ_ERR_PIPELINE, wait code of the self-test
+    assert "pipeline" in rzlib.load().rz_status_string(st).decode()
+    assert rzlib.device_status() == (0, 0)               # reading the status clears it
+    # the context is still usable: a tensor-core problem runs and matches the oracle
+    eY, eX, eH = tc_case(rzlib, L, 256, 512, 512, 1 << 17, 128, 128, torch.bfloat16, seed=3)
+    assert max(eY, eX, eH) < TOL_TC
+    with pytest.raises(rzlib.RzLinearError):
+        rzlib.selftest_bounded_wait(0, DEV)
