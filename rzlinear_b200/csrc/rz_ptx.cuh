@@ -48,16 +48,35 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+// try_wait that lets the hardware suspend the thread for up to `hint_ns` instead of spinning
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait: gives up after `limit_cycles` SM cycles (or as soon as another waiter has given
 // up), records `code` in the status word and returns false.  The caller then leaves its loop.
+// `hint_ns` > 0 is for waits that are expected to be long (an epilogue waiting for a whole main
+// loop): the thread sleeps in the barrier unit between polls instead of burning issue slots.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int code, int *status,
-                                                  long long limit_cycles)
+                                                  long long limit_cycles, uint32_t hint_ns = 0)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    const uint32_t check_mask = hint_ns ? 0x3u : 0xffu;
     for (uint32_t it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 0xffu) == 0) {
+        if (hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity)) return true;
+        if ((it & check_mask) == 0) {
             if (*reinterpret_cast<volatile int *>(status) != 0) return false;
             if (clock64() - t0 > limit_cycles) {
                 atomicCAS(status, 0, (code << 8) | 1);

@@ -22,7 +22,9 @@
 // the hash-tile offsets in registers and TMA-loads the matching rows of the slice.  TMA needs a
 // 16-byte aligned start, and a slice starts at any element, so FWD and DX read a "shadow" of the
 // hashed array: NS element-shifted copies in the compute type (NS = 8 bf16 / 4 tf32); the copy
-// whose shift equals offset mod NS holds the slice at an aligned position.  The shadow tensor map
+// whose shift equals offset mod NS holds the slice at an aligned position.  (Twice as many copies would
+// align rows to 32-byte sectors - four L2 sectors per 128-byte row instead of five, worth 8 % when emulated -
+// but the larger footprint costs more L2 misses than that; measured, not adopted.)  The shadow tensor map
 // is 3-D {element, slice row (stride BN), copy}.
 //
 // Every TMA load is a plain per-CTA copy of this GPU's memory; no kernel touches peer-GPU memory.
@@ -232,7 +234,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 if (lane == 0) {
                     for (uint32_t ci = 0; ci < nb; ++ci) {
                         const uint32_t g = it + ci, s = g % STAGES, ph = (g / STAGES) & 1;
-                        if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1, RZ_WAIT_SMEM_EMPTY, p.status, p.wait_limit)) {
+                        if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1, RZ_WAIT_SMEM_EMPTY, p.status, p.wait_limit, 2000)) {
                             ok = false;
                             it += ci;
                             break;
@@ -295,7 +297,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             decode(item, tr, tc, c_begin, c_end);
             const uint32_t buf = n_items % NBUF, tph = (n_items / NBUF) & 1;
             if (lane == 0) {
-                if (!mbar_wait_bounded(bar_tempty + 8 * buf, tph ^ 1, RZ_WAIT_TMEM_EMPTY, p.status, p.wait_limit)) ok = false;
+                if (!mbar_wait_bounded(bar_tempty + 8 * buf, tph ^ 1, RZ_WAIT_TMEM_EMPTY, p.status, p.wait_limit, 2000)) ok = false;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * RB * TILE_C;
                 for (uint32_t c = c_begin; c < c_end && ok; ++c, ++it) {
@@ -349,8 +351,10 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
             const uint32_t buf = n_items % NBUF, tph = (n_items / NBUF) & 1;
-            bool mine = mbar_wait_bounded(bar_tfull + 8 * buf, tph, RZ_WAIT_TMEM_FULL, p.status, p.wait_limit);
-            ok = __all_sync(0xffffffffu, mine);
+            // one lane per warp polls (sleeping in the barrier unit between polls); the others wait for it
+            bool mine = true;
+            if (lane == 0) mine = mbar_wait_bounded(bar_tfull + 8 * buf, tph, RZ_WAIT_TMEM_FULL, p.status, p.wait_limit, 20000);
+            ok = __shfl_sync(0xffffffffu, (int)mine, 0) != 0;
             if (!ok) break;
             tc_fence_after();
             const uint32_t rbase = tr * ITEM_R + rblk * PAIR_R + rank * TILE_R + q * 32;   // first row of this warp
@@ -626,7 +630,7 @@ int choose_config(const rz_problem *pb, int op)
     const int64_t stages = depth / (pb->precision == RZ_PREC_TF32 ? 32 : 64);
     // With two row blocks every TMEM column is an accumulator, so the epilogue cannot overlap the next
     // block's main loop; that only pays off when the contraction is long enough to amortise it.
-    if (rows >= 4 * TILE_R && stages >= 24) return 3;
+    if (rows >= 4 * TILE_R && stages >= 8) return 3;
     return rows >= 2 * TILE_R ? 2 : 1;
 }
 int config_ctas(int config) { return config == 1 ? 1 : 2; }
