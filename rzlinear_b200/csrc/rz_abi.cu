@@ -58,7 +58,7 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 bool use_tc(const rz_problem *pb, int op)
 {
     if (pb->flags & RZ_FLAG_FORCE_SIMT) return false;
-    if (pb->precision == RZ_PREC_FP32) return false;
+    if (pb->precision == RZ_PREC_FP32 && pb->io_dtype != RZ_F32) return false;   // fp32 math on bf16 data: FMA kernels
     return rz_tc_supported(pb, op);
 }
 

@@ -12,6 +12,10 @@
 //           stages 2 x 128 rows of A and 128 columns of B, i.e. 48 KB per 1024 tensor-clocks instead of
 //           32 KB per 512.  The kernels are bound by what an SM can pull from L2 (about 50 B/clk), so
 //           this is the fast configuration; it is used whenever the output has at least 512 rows.
+// SPLIT = 1 (fp32 precision on the tensor cores, RB = 1 only): operands are fp32; four extra warps split every
+//           staged tile in shared memory into hi = the tf32-representable part and lo = x - hi, and each K-step
+//           issues hi*hi + hi*lo + lo*hi (three tf32 MMAs, fp32 accumulate): fp32-grade results (the dropped
+//           lo*lo term and the rounding of lo are of relative order 2^-22) at a third of the tf32 rate.
 // Accumulators live in TMEM (512 columns): with RB = 1 two 256-column buffers alternate so the epilogue of
 // one block overlaps the main loop of the next; with RB = 2 both halves are accumulators of one block.
 // Warp 0 produces (TMA loads into a ring of 128-byte-swizzled shared-memory tiles), warp 1 issues
@@ -56,21 +60,23 @@ constexpr int GROUP_ROWS = 8;   // row tiles per rasterisation group (4 when a t
 constexpr int SMEM_EPI_WARP = 32 * 33 * 4;
 constexpr int SMEM_TABLE = 3 * BATCH * MAX_TPS * 4;
 constexpr int MAX_STAGES = 7;
-constexpr int SMEM_BARS = (2 * MAX_STAGES + 5) * 8;
+constexpr int SMEM_BARS = (3 * MAX_STAGES + 5) * 8;
 constexpr int SMEM_LIMIT = 232448;
 // per epilogue warp: a 32x33 fp32 transpose tile (DW) or a 32-row x 128-byte store staging tile (FWD, DX)
 __host__ __device__ constexpr int smem_epi(int op, int rb) { return 4 * rb * (op == OP_DW ? SMEM_EPI_WARP : 4096); }
-__host__ __device__ constexpr int stage_bytes(int ctas, int rb) { return rb * A_BLOCK_BYTES + (TILE_C / ctas) * 128; }
-__host__ __device__ constexpr int num_stages(int op, int ctas, int rb)
+__host__ __device__ constexpr int load_bytes(int ctas, int rb) { return rb * A_BLOCK_BYTES + (TILE_C / ctas) * 128; }
+__host__ __device__ constexpr int stage_bytes(int ctas, int rb, int split) { return load_bytes(ctas, rb) * (split ? 2 : 1); }
+__host__ __device__ constexpr int num_stages(int op, int ctas, int rb, int split)
 {
-    int n = (SMEM_LIMIT - 1024 - 16 - SMEM_BARS - SMEM_TABLE - smem_epi(op, rb)) / stage_bytes(ctas, rb);
+    int n = (SMEM_LIMIT - 1024 - 16 - SMEM_BARS - SMEM_TABLE - smem_epi(op, rb)) / stage_bytes(ctas, rb, split);
     return n > MAX_STAGES ? MAX_STAGES : n;
 }
-__host__ __device__ constexpr int smem_total(int op, int ctas, int rb)
+__host__ __device__ constexpr int smem_total(int op, int ctas, int rb, int split)
 {
-    return num_stages(op, ctas, rb) * stage_bytes(ctas, rb) + smem_epi(op, rb) + SMEM_TABLE + SMEM_BARS + 16 + 1024;
+    return num_stages(op, ctas, rb, split) * stage_bytes(ctas, rb, split) + smem_epi(op, rb) + SMEM_TABLE + SMEM_BARS + 16 +
+           1024;
 }
-__host__ __device__ constexpr int num_threads(int rb) { return 64 + 128 * rb; }
+__host__ __device__ constexpr int num_threads(int rb, int split) { return 64 + 128 * rb + (split ? 128 : 0); }
 
 struct TcParams {
     RzHash hash;
@@ -101,8 +107,8 @@ __device__ __forceinline__ void wait_cycles(uint32_t bar, uint32_t parity, long 
         if (clock64() - t0 > cycles) break;
 }
 
-template <int OP, bool TF32, int CTAS, int RB>
-__global__ void __launch_bounds__(num_threads(RB), 1)
+template <int OP, bool TF32, int CTAS, int RB, int SPLIT>
+__global__ void __launch_bounds__(num_threads(RB, SPLIT), 1)
 rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
     constexpr int ES = TF32 ? 4 : 2;        // operand element size
@@ -114,12 +120,16 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     constexpr int B_COLS = TILE_C / CTAS;   // columns of B this CTA stages
     constexpr int B_BYTES = B_COLS * 128;
     constexpr int A_BYTES = RB * A_BLOCK_BYTES;
-    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int STAGES = num_stages(OP, CTAS, RB);
+    constexpr int LOAD_BYTES = A_BYTES + B_BYTES;                 // what TMA brings per stage and CTA
+    constexpr int STAGE_BYTES = LOAD_BYTES * (SPLIT ? 2 : 1);     // SPLIT: the lo parts sit LOAD_BYTES above the hi parts
+    constexpr int STAGES = num_stages(OP, CTAS, RB, SPLIT);
+    constexpr bool PAIR_LOADS = (CTAS == 2) && !SPLIT;            // loads of both CTAs counted on the leader's barrier
+    constexpr int EPI_WARPS = 4 * RB;
+    static_assert(!SPLIT || (TF32 && RB == 1), "split precision: fp32 operands, one row block");
     constexpr int SMEM_RING = STAGES * STAGE_BYTES;
     constexpr int SMEM_EPI_OP = smem_epi(OP, RB);
     constexpr int NBUF = 2 / RB;            // accumulator sets in TMEM (2: double-buffered, 1: none spare)
-    static_assert(STAGE_BYTES == stage_bytes(CTAS, RB), "stage size");
+    static_assert(STAGE_BYTES == stage_bytes(CTAS, RB, SPLIT), "stage size");
     static_assert(RB == 1 || CTAS == 2, "two row blocks only with CTA pairs");
     constexpr int A_ATOMS = TILE_R / EPR;
     constexpr int B_ATOMS = B_COLS / EPR;
@@ -140,6 +150,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     const uint32_t bar_tfull = bars + 16 * MAX_STAGES;        // [2]       one set per CTA
     const uint32_t bar_tempty = bars + 16 * MAX_STAGES + 16;  // [2]       used in the leader CTA
     const uint32_t bar_drain = bars + 16 * MAX_STAGES + 32;   // [1]
+    const uint32_t bar_split = bars + 16 * MAX_STAGES + 40;   // [STAGES]  SPLIT only, used in the leader CTA
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + SMEM_RING + SMEM_EPI_OP + SMEM_TABLE + SMEM_BARS);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -151,6 +162,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
+            mbar_init(bar_split + 8 * s, 4 * CTAS);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_tfull + 8 * b, 1);
@@ -197,7 +209,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         uint32_t it = 0;  // stages armed so far
         // transaction bytes of a stage are counted on the leader's barrier
         uint32_t full_base = bar_full;
-        if (CTAS == 2) full_base = mapa_cluster(bar_full, 0);
+        if (PAIR_LOADS) full_base = mapa_cluster(bar_full, 0);
         for (uint32_t item = first_item; item < p.total_items && ok; item += item_stride) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
@@ -241,12 +253,16 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                         }
                         const uint32_t full = full_base + 8 * s;
                         const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
-                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, STAGE_BYTES * CTAS);
+                        if (PAIR_LOADS) {
+                            if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, LOAD_BYTES * CTAS);
+                        } else {
+                            mbar_arrive_expect_tx(bar_full + 8 * s, LOAD_BYTES);
+                        }
                         const uint32_t d0 = (cb + ci) * KC;  // contraction start of this stage
                         if (OP == OP_FWD || OP == OP_DX) {
 #pragma unroll
                             for (int r = 0; r < RB; ++r) {
-                                if (CTAS == 2)
+                                if (PAIR_LOADS)
                                     tma_load_2d_pair(sa + r * A_BLOCK_BYTES, &mapA, full, (int32_t)d0, (int32_t)(row0 + r * PAIR_R));
                                 else
                                     tma_load_2d(sa, &mapA, full, (int32_t)d0, (int32_t)row0);
@@ -256,7 +272,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                             for (uint32_t j = 0; j < tps; ++j) {
                                 const int32_t x = (int32_t)tab_x[ci * MAX_TPS + j], y = (int32_t)tab_y[ci * MAX_TPS + j],
                                               z = (int32_t)tab_z[ci * MAX_TPS + j];
-                                if (CTAS == 2) tma_load_3d_pair(sb + j * box_bytes, &mapB, full, x, y, z);
+                                if (PAIR_LOADS) tma_load_3d_pair(sb + j * box_bytes, &mapB, full, x, y, z);
                                 else tma_load_3d(sb + j * box_bytes, &mapB, full, x, y, z);
                             }
                         } else {
@@ -266,13 +282,13 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                                 for (int a = 0; a < A_ATOMS; ++a) {
                                     const uint32_t dst = sa + r * A_BLOCK_BYTES + a * ATOM;
                                     const int32_t x = (int32_t)(row0 + r * PAIR_R + a * EPR);
-                                    if (CTAS == 2) tma_load_2d_pair(dst, &mapA, full, x, (int32_t)d0);
+                                    if (PAIR_LOADS) tma_load_2d_pair(dst, &mapA, full, x, (int32_t)d0);
                                     else tma_load_2d(dst, &mapA, full, x, (int32_t)d0);
                                 }
                             }
 #pragma unroll
                             for (int j = 0; j < B_ATOMS; ++j) {
-                                if (CTAS == 2) tma_load_2d_pair(sb + j * ATOM, &mapB, full, (int32_t)(col0 + j * EPR), (int32_t)d0);
+                                if (PAIR_LOADS) tma_load_2d_pair(sb + j * ATOM, &mapB, full, (int32_t)(col0 + j * EPR), (int32_t)d0);
                                 else tma_load_2d(sb + j * ATOM, &mapB, full, (int32_t)(col0 + j * EPR), (int32_t)d0);
                             }
                         }
@@ -284,7 +300,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 it = __shfl_sync(0xffffffffu, it, 0);
             }
         }
-        if (!ok && lane == 0 && rank == 0) {
+        if (!ok && lane == 0 && (rank == 0 || !PAIR_LOADS)) {
             // give the loads already issued time to land before the CTA retires
             const uint32_t lo = it > STAGES ? it - STAGES : 0;
             for (uint32_t g = lo; g < it; ++g) wait_cycles(bar_full + 8 * (g % STAGES), (g / STAGES) & 1, 4000000);
@@ -302,7 +318,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 const uint32_t d_tmem = tmem_base + buf * RB * TILE_C;
                 for (uint32_t c = c_begin; c < c_end && ok; ++c, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (!mbar_wait_bounded(bar_full + 8 * s, ph, RZ_WAIT_SMEM_FULL, p.status, p.wait_limit)) {
+                    if (!mbar_wait_bounded((SPLIT ? bar_split : bar_full) + 8 * s, ph, RZ_WAIT_SMEM_FULL, p.status, p.wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -318,6 +334,18 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                                 make_desc_sw128(sa + r * A_BLOCK_BYTES + kk * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
                             if (CTAS == 2) tc_mma_pair<TF32>(d_tmem + r * TILE_C, ad, bd, p.idesc, acc);
                             else tc_mma<TF32>(d_tmem, ad, bd, p.idesc, acc);
+                            if (SPLIT) {
+                                // + hi(A) * lo(B) + lo(A) * hi(B)
+                                const uint64_t ad_lo = make_desc_sw128(sa + LOAD_BYTES + kk * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
+                                const uint64_t bd_lo = make_desc_sw128(sb + LOAD_BYTES + kk * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
+                                if (CTAS == 2) {
+                                    tc_mma_pair<TF32>(d_tmem, ad, bd_lo, p.idesc, 1u);
+                                    tc_mma_pair<TF32>(d_tmem, ad_lo, bd, p.idesc, 1u);
+                                } else {
+                                    tc_mma<TF32>(d_tmem, ad, bd_lo, p.idesc, 1u);
+                                    tc_mma<TF32>(d_tmem, ad_lo, bd, p.idesc, 1u);
+                                }
+                            }
                         }
                     }
                     // frees this stage in both CTAs once the MMAs have read it
@@ -339,7 +367,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             else tc_commit(bar_drain);
             wait_cycles(bar_drain, 0, 20000000);
         }
-    } else {
+    } else if (warp < 2 + EPI_WARPS) {
         // ===================== epilogue (both CTAs; each drains its own 128 rows) =====================
         const uint32_t q = warp & 3;          // TMEM lane quarter this warp may read
         const uint32_t rblk = (warp - 2) >> 2;  // which accumulator (row block) of the item this warp drains
@@ -448,6 +476,46 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         }
     }
 
+    else if (SPLIT) {
+        // ===================== splitter (SPLIT only): hi/lo parts of every staged tile =====================
+        const uint32_t tid = threadIdx.x - (2 + EPI_WARPS) * 32;   // 0..127
+        uint32_t split_base = bar_split;
+        if (CTAS == 2) split_base = mapa_cluster(bar_split, 0);
+        uint32_t it = 0;
+        for (uint32_t item = first_item; item < p.total_items && ok; item += item_stride) {
+            uint32_t tr, tc, c_begin, c_end;
+            decode(item, tr, tc, c_begin, c_end);
+            for (uint32_t c = c_begin; c < c_end && ok; ++c, ++it) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                bool mine = mbar_wait_bounded(bar_full + 8 * s, ph, RZ_WAIT_SMEM_FULL, p.status, p.wait_limit, 1000);
+                ok = __all_sync(0xffffffffu, mine);
+                if (!ok) break;
+                uint4 *hi = reinterpret_cast<uint4 *>(smem_gen + s * STAGE_BYTES);
+                uint4 *lo = reinterpret_cast<uint4 *>(smem_gen + s * STAGE_BYTES + LOAD_BYTES);
+#pragma unroll 4
+                for (uint32_t v = tid; v < LOAD_BYTES / 16; v += 128) {
+                    uint4 x = hi[v], h, l;
+                    h.x = x.x & 0xFFFFE000u;
+                    h.y = x.y & 0xFFFFE000u;
+                    h.z = x.z & 0xFFFFE000u;
+                    h.w = x.w & 0xFFFFE000u;
+                    l.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(h.x));
+                    l.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(h.y));
+                    l.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(h.z));
+                    l.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(h.w));
+                    hi[v] = h;
+                    lo[v] = l;
+                }
+                fence_proxy_async();   // the tensor core reads these tiles through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    if (CTAS == 2) mbar_arrive_cluster(split_base + 8 * s);
+                    else mbar_arrive(bar_split + 8 * s);
+                }
+            }
+        }
+    }
+
     tc_fence_before();
     __syncthreads();
     if (CTAS == 2) cluster_sync_all();   // neither CTA retires while the peer may still signal or read it
@@ -482,9 +550,10 @@ __device__ __forceinline__ uint32_t to_tf32(float v)
 }
 
 // copy s, element j  =  convert(hashed[j + s])   (0 past the end); one thread writes NS elements of every copy
+// `raw` (fp32 elements only): keep every mantissa bit, for the split-precision kernels that form hi/lo themselves
 template <bool TF32>
 __global__ void rz_shadow_kernel(const float *__restrict__ hashed, uint8_t *__restrict__ shadow, uint32_t H, uint32_t Hc,
-                                 size_t copy_stride)
+                                 size_t copy_stride, int raw)
 {
     constexpr int NS = TF32 ? 4 : 8;
     const uint32_t groups = Hc / NS;
@@ -497,10 +566,10 @@ __global__ void rz_shadow_kernel(const float *__restrict__ hashed, uint8_t *__re
         for (int s = 0; s < NS; ++s) {
             uint4 u;
             if (TF32) {
-                u.x = to_tf32(v[s + 0]);
-                u.y = to_tf32(v[s + 1]);
-                u.z = to_tf32(v[s + 2]);
-                u.w = to_tf32(v[s + 3]);
+                u.x = raw ? __float_as_uint(v[s + 0]) : to_tf32(v[s + 0]);
+                u.y = raw ? __float_as_uint(v[s + 1]) : to_tf32(v[s + 1]);
+                u.z = raw ? __float_as_uint(v[s + 2]) : to_tf32(v[s + 2]);
+                u.w = raw ? __float_as_uint(v[s + 3]) : to_tf32(v[s + 3]);
             } else {
                 __nv_bfloat162 h0 = __floats2bfloat162_rn(v[s + 0], v[s + 1]);
                 __nv_bfloat162 h1 = __floats2bfloat162_rn(v[s + 2], v[s + 3]);
@@ -562,7 +631,7 @@ struct Geometry {
 Geometry geometry(const rz_problem *pb)
 {
     Geometry g;
-    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    const bool tf32 = pb->precision != RZ_PREC_BF16;   // fp32 elements (tf32 and split-precision fp32)
     g.es = tf32 ? 4 : 2;
     g.epr = 128 / g.es;
     g.ns = 16 / g.es;
@@ -627,10 +696,10 @@ int choose_config(const rz_problem *pb, int op)
     if (forced >= 1 && forced <= 3) return (int)forced;
     const int64_t rows = (op == RZ_OP_BACKWARD_WEIGHT) ? pb->K : pb->M;
     const int64_t depth = (op == RZ_OP_FORWARD) ? pb->K : (op == RZ_OP_BACKWARD_INPUT ? pb->N : pb->M);
-    const int64_t stages = depth / (pb->precision == RZ_PREC_TF32 ? 32 : 64);
+    const int64_t stages = depth / (pb->precision == RZ_PREC_BF16 ? 64 : 32);
     // With two row blocks every TMEM column is an accumulator, so the epilogue cannot overlap the next
     // block's main loop; that only pays off when the contraction is long enough to amortise it.
-    if (rows >= 4 * TILE_R && stages >= 8) return 3;
+    if (rows >= 4 * TILE_R && stages >= 8 && pb->precision != RZ_PREC_FP32) return 3;
     return rows >= 2 * TILE_R ? 2 : 1;
 }
 int config_ctas(int config) { return config == 1 ? 1 : 2; }
@@ -638,13 +707,10 @@ int config_ctas(int config) { return config == 1 ? 1 : 2; }
 uint32_t dx_box_rows(const rz_problem *pb, int ctas)
 {
     const uint32_t bcols = (uint32_t)(TILE_C / ctas);
-    uint32_t br = (uint32_t)pb->BK < bcols ? (uint32_t)pb->BK : bcols;
-    const uint32_t forced = env_u32("RZ_TC_BR", 0);
-    if (forced && forced <= br && br % forced == 0 && TILE_C / ctas / forced <= MAX_TPS) br = forced;
-    return br;
+    return (uint32_t)pb->BK < bcols ? (uint32_t)pb->BK : bcols;
 }
 
-template <int OP, bool TF32, int CTAS, int RB>
+template <int OP, bool TF32, int CTAS, int RB, int SPLIT>
 int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p)
 {
     const rz_problem *pb = c.pb;
@@ -653,7 +719,7 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     constexpr int KC = EPR;
     constexpr int PAIR_R = TILE_R * CTAS;
     constexpr int ITEM_R = PAIR_R * RB;
-    constexpr int NTHREADS = num_threads(RB);
+    constexpr int NTHREADS = num_threads(RB, SPLIT);
     p.hash = c.hash;
     p.M = (uint32_t)pb->M;
     p.K = (uint32_t)pb->K;
@@ -668,8 +734,8 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.group_rows = env_u32("RZ_TC_GROUP", GROUP_ROWS / RB);
     if (p.group_rows < 1) p.group_rows = 1;
 
-    auto kern = rz_tc_kernel<OP, TF32, CTAS, RB>;
-    constexpr int SMEM_TOTAL = smem_total(OP, CTAS, RB);
+    auto kern = rz_tc_kernel<OP, TF32, CTAS, RB, SPLIT>;
+    constexpr int SMEM_TOTAL = smem_total(OP, CTAS, RB, SPLIT);
     static_assert(SMEM_TOTAL <= SMEM_LIMIT, "shared memory budget");
     int st = rz_record_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL),
                             "set max dynamic shared memory");
@@ -750,12 +816,15 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
 template <int OP>
 int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, int config)
 {
-    const bool tf32 = c.pb->precision == RZ_PREC_TF32;
+    const int prec = c.pb->precision;
+    if (prec == RZ_PREC_FP32)   // split precision: fp32 operands, three tf32 MMAs per product
+        return config >= 2 ? launch_tc<OP, true, 2, 1, 1>(c, mapA, mapB, p) : launch_tc<OP, true, 1, 1, 1>(c, mapA, mapB, p);
+    const bool tf32 = prec == RZ_PREC_TF32;
     if (config == 3)
-        return tf32 ? launch_tc<OP, true, 2, 2>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 2>(c, mapA, mapB, p);
+        return tf32 ? launch_tc<OP, true, 2, 2, 0>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 2, 0>(c, mapA, mapB, p);
     if (config == 2)
-        return tf32 ? launch_tc<OP, true, 2, 1>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 1>(c, mapA, mapB, p);
-    return tf32 ? launch_tc<OP, true, 1, 1>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1>(c, mapA, mapB, p);
+        return tf32 ? launch_tc<OP, true, 2, 1, 0>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 1, 0>(c, mapA, mapB, p);
+    return tf32 ? launch_tc<OP, true, 1, 1, 0>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1, 0>(c, mapA, mapB, p);
 }
 
 // 2-D map over a row-major matrix [rows][cols] of the operand type
@@ -773,7 +842,7 @@ int map_matrix(CUtensorMap *map, bool tf32, bool mn_major, const void *base, uin
 int map_shadow(CUtensorMap *map, const rz_problem *pb, bool mn_major, const void *shadow, uint32_t box_rows)
 {
     const Geometry g = geometry(pb);
-    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    const bool tf32 = pb->precision != RZ_PREC_BF16;
     uint64_t dims[3] = {g.Hc, (uint64_t)pb->BK, (uint64_t)g.ns};
     uint64_t strides[2] = {(uint64_t)pb->BN * g.es, (uint64_t)g.copy_stride};
     uint32_t box[3] = {(uint32_t)g.epr, box_rows, 1};
@@ -794,7 +863,6 @@ int rz_tc_wait_selftest(long long limit_cycles, cudaStream_t stream)
 bool rz_tc_supported(const rz_problem *pb, int op)
 {
     (void)op;
-    if (pb->precision != RZ_PREC_TF32 && pb->precision != RZ_PREC_BF16) return false;
     const Geometry g = geometry(pb);
     if (pb->BK % g.epr || pb->BN % g.epr) return false;
     if (pb->BK <= 128 ? (128 % pb->BK != 0) : (pb->BK % 128 != 0)) return false;  // whole B boxes per hash tile
@@ -815,10 +883,11 @@ int rz_tc_shadow_refresh(const RzLaunchCtx &c, const float *hashed, void *shadow
     const uint32_t groups = g.Hc / g.ns;
     uint32_t blocks = (groups + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    if (c.pb->precision == RZ_PREC_TF32)
-        rz_shadow_kernel<true><<<blocks, 256, 0, c.stream>>>(hashed, (uint8_t *)shadow, (uint32_t)c.pb->H, g.Hc, g.copy_stride);
+    if (c.pb->precision != RZ_PREC_BF16)
+        rz_shadow_kernel<true><<<blocks, 256, 0, c.stream>>>(hashed, (uint8_t *)shadow, (uint32_t)c.pb->H, g.Hc, g.copy_stride,
+                                                            c.pb->precision == RZ_PREC_FP32 ? 1 : 0);
     else
-        rz_shadow_kernel<false><<<blocks, 256, 0, c.stream>>>(hashed, (uint8_t *)shadow, (uint32_t)c.pb->H, g.Hc, g.copy_stride);
+        rz_shadow_kernel<false><<<blocks, 256, 0, c.stream>>>(hashed, (uint8_t *)shadow, (uint32_t)c.pb->H, g.Hc, g.copy_stride, 0);
     rz_count_launch(1);
     return rz_record_cuda(cudaGetLastError(), "shadow refresh launch");
 }
@@ -839,7 +908,7 @@ int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float l
 int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const float *bias, void *Y)
 {
     const rz_problem *pb = c.pb;
-    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    const bool tf32 = pb->precision != RZ_PREC_BF16;
     const Geometry g = geometry(pb);
     CUtensorMap mapA, mapB;
     int st = map_matrix(&mapA, tf32, false, X, pb->M, pb->K, g.epr, TILE_R);
@@ -856,7 +925,7 @@ int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const
 int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shadow, void *dX)
 {
     const rz_problem *pb = c.pb;
-    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    const bool tf32 = pb->precision != RZ_PREC_BF16;
     const Geometry g = geometry(pb);
     CUtensorMap mapA, mapB;
     int st = map_matrix(&mapA, tf32, false, dY, pb->M, pb->N, g.epr, TILE_R);
@@ -873,7 +942,7 @@ int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shado
 int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, float *dH)
 {
     const rz_problem *pb = c.pb;
-    const bool tf32 = pb->precision == RZ_PREC_TF32;
+    const bool tf32 = pb->precision != RZ_PREC_BF16;
     const Geometry g = geometry(pb);
     CUtensorMap mapA, mapB;
     int st = map_matrix(&mapA, tf32, true, X, pb->M, pb->K, g.epr, g.epr);

@@ -226,12 +226,13 @@ def test_module_skips_input_grad_and_shares_weight():
 # ---------------------------------------------------------------------------------------------
 # tensor-core paths
 # ---------------------------------------------------------------------------------------------
-def tc_case(rzlib, L, M, K, N, H, BK, BN, dtype, seed, alpha=1.0, mode=0):
-    allow_tf32 = dtype == torch.float32
+def tc_case(rzlib, L, M, K, N, H, BK, BN, dtype, seed, alpha=1.0, mode=0, allow_tf32=None):
+    if allow_tf32 is None:
+        allow_tf32 = dtype == torch.float32
     R = seeded_R(seed) if mode == 0 else seeded_R(seed, 45007)
     X, dY, h = make_inputs(M, K, N, H, seed, dtype)
     pb = rzlib.make_problem(M, K, N, H, BK, BN, R, mode, 1 if dtype == torch.bfloat16 else 0,
-                            2 if dtype == torch.bfloat16 else 1, alpha)
+                            2 if dtype == torch.bfloat16 else (1 if allow_tf32 else 0), alpha)
     for op in (0, 1, 2):
         assert rzlib.plan(pb, op) == rzlib.PATH_TCGEN05
     Y, dX, dH = run_three(L, X.to(DEV), dY.to(DEV), h.to(DEV), N, BK, BN, R, mode, alpha, allow_tf32)
@@ -264,6 +265,18 @@ def test_bf16_tensor_core_path(rzlib, L, M, K, N, H, BK, BN):
 def test_tf32_tensor_core_path(rzlib, L, M, K, N, H, BK, BN):
     eY, eX, eH = tc_case(rzlib, L, M, K, N, H, BK, BN, torch.float32, seed=M + K + BK)
     assert eY < TOL_TC and eX < TOL_TC and eH < TOL_TC, (eY, eX, eH)
+
+
+@pytest.mark.parametrize("M,K,N,H,BK,BN", [
+    (256, 256, 512, 1 << 17, 64, 64),      # CTA pair
+    (1024, 1024, 1024, 65536, 32, 32),     # the fp32 baseline configuration
+    (200, 132, 260, 50001, 32, 64),        # single CTA, ragged
+    (640, 512, 384, 1 << 16, 128, 32),
+])
+def test_fp32_precision_on_tensor_cores(rzlib, L, M, K, N, H, BK, BN):
+    # fp32 in, fp32-grade out: split operands (hi + lo), three tf32 MMAs per product; the fp32 bar applies
+    eY, eX, eH = tc_case(rzlib, L, M, K, N, H, BK, BN, torch.float32, seed=M + N + BN, alpha=1.25, allow_tf32=False)
+    assert eY < TOL_FP32 and eX < TOL_FP32 and eH < TOL_FP32, (eY, eX, eH)
 
 
 def test_tensor_core_two_level_hash_and_collisions(rzlib, L):

@@ -109,8 +109,12 @@ def test_null_pointers_are_rejected_before_any_launch(rzlib):
 
 
 def test_plan_selects_kernel_family(rzlib):
-    # fp32 precision always runs the FMA kernels
-    assert rzlib.plan(_pb(rzlib, M=1024, K=1024, N=1024, H=65536, BK=32, BN=32), 0) == rzlib.PATH_SIMT
+    # fp32 precision on fp32 data: tensor cores with split (hi/lo) operands when the shape is tile-aligned,
+    # FMA kernels otherwise (small batch, hash tile not a multiple of 32, forced)
+    assert rzlib.plan(_pb(rzlib, M=1024, K=1024, N=1024, H=65536, BK=32, BN=32), 0) == rzlib.PATH_TCGEN05
+    assert rzlib.plan(_pb(rzlib, M=64, K=1024, N=1024, H=65536, BK=32, BN=32), 0) == rzlib.PATH_SIMT
+    assert rzlib.plan(_pb(rzlib, M=1024, K=1024, N=1024, H=65536, BK=16, BN=32), 0) == rzlib.PATH_SIMT
+    assert rzlib.plan(_pb(rzlib, M=1024, K=1024, N=1024, H=65536, BK=32, BN=32, flags=rzlib.FLAG_FORCE_SIMT), 0) == rzlib.PATH_SIMT
     # tile-aligned bf16 / tf32 problems take the tensor-core kernels
     big = dict(M=8192, K=8192, N=8192, H=1 << 22, BK=128, BN=128)
     for op in (0, 1, 2):
