@@ -386,23 +386,58 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             if (!ok) break;
             tc_fence_after();
             const uint32_t rbase = tr * ITEM_R + rblk * PAIR_R + rank * TILE_R + q * 32;   // first row of this warp
+            // Weight gradient: the block's eight 32-column chunks of this warp's rows go to slices of the hashed
+            // gradient.  Chunks that land on exactly the same addresses (tiles of one tile row whose offsets
+            // collide, same position inside the tile) are summed in registers first, so a collision costs one
+            // set of reductions instead of one per tile.  Lane c (< 8) holds the destination of chunk c.
+            uint32_t key_off = 0, key_rel = 0, eqmask = 0;
+            if (OP == OP_DW) {
+                const uint32_t pk = rbase / (uint32_t)p.hash.BK;
+                if (lane < TILE_C / 32) {
+                    const uint32_t ccol = tc * TILE_C + lane * 32, pn = ccol / (uint32_t)p.hash.BN;
+                    key_rel = ccol - pn * (uint32_t)p.hash.BN;
+                    key_off = (uint32_t)rz_tile_offset(p.hash, pk, pn);
+                }
+#pragma unroll
+                for (int c2 = 0; c2 < TILE_C / 32; ++c2) {
+                    const uint32_t o2 = __shfl_sync(0xffffffffu, key_off, c2), r2 = __shfl_sync(0xffffffffu, key_rel, c2);
+                    if (o2 == key_off && r2 == key_rel) eqmask |= 1u << c2;
+                }
+            }
 #pragma unroll 1
             for (int c = 0; c < TILE_C / 32; ++c) {
                 uint32_t v[32];
+                uint32_t same = 0;
+                if (OP == OP_DW) {
+                    same = __shfl_sync(0xffffffffu, eqmask, c);
+                    if (same & ((1u << c) - 1u)) continue;   // already merged into an earlier chunk
+                }
                 tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + (buf * RB + rblk) * TILE_C + c * 32, v);
                 tmem_ld_wait();
                 const uint32_t col = tc * TILE_C + c * 32;
                 if (OP == OP_DW) {
+                    float acc[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) scratch[lane * 33 + j] = __uint_as_float(v[j]) * p.alpha;
+                    for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(v[j]);
+                    bool col_ok = col + lane < p.N;
+                    uint32_t rest = same & ~((2u << c) - 1u);   // later chunks with the same destination
+                    while (rest) {
+                        const int c2 = __ffs(rest) - 1;
+                        rest &= rest - 1;
+                        tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + (buf * RB + rblk) * TILE_C + c2 * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+                        col_ok = col_ok || (tc * TILE_C + c2 * 32 + lane < p.N);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) scratch[lane * 33 + j] = acc[j] * p.alpha;
                     __syncwarp();
                     const uint32_t kb = rbase;
-                    if (kb < p.K && col < p.N) {
-                        const uint32_t pk = kb / (uint32_t)p.hash.BK, pn = col / (uint32_t)p.hash.BN;
-                        float *dst = p.dH + rz_tile_offset(p.hash, pk, pn) +
-                                     (uint64_t)(kb - pk * (uint32_t)p.hash.BK) * (uint32_t)p.hash.BN +
-                                     (col - pn * (uint32_t)p.hash.BN) + lane;
-                        const bool col_ok = col + lane < p.N;
+                    const uint32_t off = __shfl_sync(0xffffffffu, key_off, c), rel = __shfl_sync(0xffffffffu, key_rel, c);
+                    if (kb < p.K) {
+                        const uint32_t pk = kb / (uint32_t)p.hash.BK;
+                        float *dst = p.dH + off + (uint64_t)(kb - pk * (uint32_t)p.hash.BK) * (uint32_t)p.hash.BN + rel + lane;
                         const uint32_t nrow = min(32u, p.K - kb);
                         for (uint32_t rr = 0; rr < nrow; ++rr)
                             if (col_ok) atomicAdd(dst + (size_t)rr * (uint32_t)p.hash.BN, scratch[rr * 33 + lane]);

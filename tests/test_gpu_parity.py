@@ -282,14 +282,24 @@ def test_fp32_precision_on_tensor_cores(rzlib, L, M, K, N, H, BK, BN):
 def test_tensor_core_two_level_hash_and_collisions(rzlib, L):
     eY, eX, eH = tc_case(rzlib, L, 256, 512, 512, 1 << 16, 64, 64, torch.bfloat16, seed=9, mode=1)
     assert eY < TOL_TC and eX < TOL_TC and eH < TOL_TC, (eY, eX, eH)
-    # all tiles of a row collide (R2 = 0 mod P)
-    M, K, N, H, BK, BN = 256, 256, 512, 40000, 64, 64
-    R = [LARGE_PRIME, 99, LARGE_PRIME, 12345, 0, 0, 0, 0]
-    X, dY, h = make_inputs(M, K, N, H, 4, torch.bfloat16)
-    Y, dX, dH = run_three(L, X.to(DEV), dY.to(DEV), h.to(DEV), N, BK, BN, R, 0)
-    hf = o.bf16_round(h.numpy())
-    assert o.rel_l2(Y, o.forward(X.float().numpy(), hf, N, BK, BN, R, 0)) < TOL_TC
-    assert o.rel_l2(dH, o.backward_weight(X.float().numpy(), dY.float().numpy(), H, BK, BN, R, 0)) < TOL_TC
+    # colliding tiles, merged in registers by the weight-gradient epilogue before the reductions:
+    #   R2 = 0 mod P           -> all tiles of a tile row share one slice
+    #   R2 = (H - BK*BN) / 2   -> every second tile of a tile row shares a slice
+    #   R2 = 100               -> neighbouring slices overlap partly (left to the L2 atomics)
+    M, K, N, H, BK, BN = 512, 256, 768, 40000, 64, 64
+    for R2 in (LARGE_PRIME, (H - BK * BN) // 2, 100):
+        R = [LARGE_PRIME, 99, R2, 12345, 0, 0, 0, 0]
+        off = o.tile_offsets(K, N, H, BK, BN, R, 0)
+        if R2 == LARGE_PRIME:
+            assert (off == off[:, :1]).all()
+        elif R2 != 100:
+            assert (off[:, 0] == off[:, 2]).all() and (off[:, 0] != off[:, 1]).all()
+        X, dY, h = make_inputs(M, K, N, H, 4, torch.bfloat16)
+        Y, dX, dH = run_three(L, X.to(DEV), dY.to(DEV), h.to(DEV), N, BK, BN, R, 0)
+        hf = o.bf16_round(h.numpy())
+        assert o.rel_l2(Y, o.forward(X.float().numpy(), hf, N, BK, BN, R, 0)) < TOL_TC
+        assert o.rel_l2(dX, o.backward_input(dY.float().numpy(), hf, K, BK, BN, R, 0)) < TOL_TC
+        assert o.rel_l2(dH, o.backward_weight(X.float().numpy(), dY.float().numpy(), H, BK, BN, R, 0)) < TOL_TC
     check_status(rzlib)
 
 
