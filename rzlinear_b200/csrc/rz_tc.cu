@@ -49,7 +49,7 @@ namespace {
 constexpr int OP_FWD = 0, OP_DX = 1, OP_DW = 2;
 
 constexpr int TILE_R = 128;  // rows per CTA and accumulator (MMA M = 128 * CTAS)
-constexpr int TILE_C = 256;  // MMA N
+constexpr int TILE_C_MAX = 256;  // widest block (MMA N); narrower blocks (128, 64) serve small grids
 constexpr int A_BLOCK_BYTES = 16384;  // one 128-row block of A per stage
 constexpr int BATCH = 8;     // pipeline stages per hash batch of the producer warp
 constexpr int MAX_TPS = 8;   // B boxes per stage at most
@@ -64,17 +64,17 @@ constexpr int SMEM_BARS = (3 * MAX_STAGES + 5) * 8;
 constexpr int SMEM_LIMIT = 232448;
 // per epilogue warp: a 32x33 fp32 transpose tile (DW) or a 32-row x 128-byte store staging tile (FWD, DX)
 __host__ __device__ constexpr int smem_epi(int op, int rb) { return 4 * rb * (op == OP_DW ? SMEM_EPI_WARP : 4096); }
-__host__ __device__ constexpr int load_bytes(int ctas, int rb) { return rb * A_BLOCK_BYTES + (TILE_C / ctas) * 128; }
-__host__ __device__ constexpr int stage_bytes(int ctas, int rb, int split) { return load_bytes(ctas, rb) * (split ? 2 : 1); }
-__host__ __device__ constexpr int num_stages(int op, int ctas, int rb, int split)
+__host__ __device__ constexpr int load_bytes(int ctas, int rb, int nc) { return rb * A_BLOCK_BYTES + (nc / ctas) * 128; }
+__host__ __device__ constexpr int stage_bytes(int ctas, int rb, int split, int nc) { return load_bytes(ctas, rb, nc) * (split ? 2 : 1); }
+__host__ __device__ constexpr int num_stages(int op, int ctas, int rb, int split, int nc)
 {
-    int n = (SMEM_LIMIT - 1024 - 16 - SMEM_BARS - SMEM_TABLE - smem_epi(op, rb)) / stage_bytes(ctas, rb, split);
+    int n = (SMEM_LIMIT - 1024 - 16 - SMEM_BARS - SMEM_TABLE - smem_epi(op, rb)) / stage_bytes(ctas, rb, split, nc);
     return n > MAX_STAGES ? MAX_STAGES : n;
 }
-__host__ __device__ constexpr int smem_total(int op, int ctas, int rb, int split)
+__host__ __device__ constexpr int smem_total(int op, int ctas, int rb, int split, int nc)
 {
-    return num_stages(op, ctas, rb, split) * stage_bytes(ctas, rb, split) + smem_epi(op, rb) + SMEM_TABLE + SMEM_BARS + 16 +
-           1024;
+    return num_stages(op, ctas, rb, split, nc) * stage_bytes(ctas, rb, split, nc) + smem_epi(op, rb) + SMEM_TABLE + SMEM_BARS +
+           16 + 1024;
 }
 __host__ __device__ constexpr int num_threads(int rb, int split) { return 64 + 128 * rb + (split ? 128 : 0); }
 
@@ -107,7 +107,7 @@ __device__ __forceinline__ void wait_cycles(uint32_t bar, uint32_t parity, long 
         if (clock64() - t0 > cycles) break;
 }
 
-template <int OP, bool TF32, int CTAS, int RB, int SPLIT>
+template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC>
 __global__ void __launch_bounds__(num_threads(RB, SPLIT), 1)
 rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
@@ -117,19 +117,22 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     constexpr int NS = 16 / ES;             // shifted shadow copies
     constexpr int MMAS = 4;                 // tcgen05.mma per stage (K = 16 bf16 / 8 tf32 each)
     constexpr int ATOM = KC * 128;          // bytes of one 128-byte-wide column block of an MN-major tile
+    constexpr int TILE_C = NC;              // columns of the block (MMA N)
     constexpr int B_COLS = TILE_C / CTAS;   // columns of B this CTA stages
     constexpr int B_BYTES = B_COLS * 128;
     constexpr int A_BYTES = RB * A_BLOCK_BYTES;
     constexpr int LOAD_BYTES = A_BYTES + B_BYTES;                 // what TMA brings per stage and CTA
     constexpr int STAGE_BYTES = LOAD_BYTES * (SPLIT ? 2 : 1);     // SPLIT: the lo parts sit LOAD_BYTES above the hi parts
-    constexpr int STAGES = num_stages(OP, CTAS, RB, SPLIT);
+    constexpr int STAGES = num_stages(OP, CTAS, RB, SPLIT, NC);
     constexpr bool PAIR_LOADS = (CTAS == 2) && !SPLIT;            // loads of both CTAs counted on the leader's barrier
     constexpr int EPI_WARPS = 4 * RB;
     static_assert(!SPLIT || (TF32 && RB == 1), "split precision: fp32 operands, one row block");
     constexpr int SMEM_RING = STAGES * STAGE_BYTES;
     constexpr int SMEM_EPI_OP = smem_epi(OP, RB);
     constexpr int NBUF = 2 / RB;            // accumulator sets in TMEM (2: double-buffered, 1: none spare)
-    static_assert(STAGE_BYTES == stage_bytes(CTAS, RB, SPLIT), "stage size");
+    static_assert(STAGE_BYTES == stage_bytes(CTAS, RB, SPLIT, NC), "stage size");
+    static_assert(NC == 256 || (CTAS == 1 && RB == 1), "narrow blocks: single CTA only");
+    static_assert(2 * RB * NC <= 512 || RB == 2, "TMEM columns");
     static_assert(RB == 1 || CTAS == 2, "two row blocks only with CTA pairs");
     constexpr int A_ATOMS = TILE_R / EPR;
     constexpr int B_ATOMS = B_COLS / EPR;
@@ -722,30 +725,78 @@ uint32_t env_u32(const char *name, uint32_t dflt)
     return s ? (uint32_t)strtoul(s, nullptr, 0) : dflt;
 }
 
-// Kernel configuration: 1 = one CTA per 128x256 block, 2 = CTA pair per 256x256 block, 3 = CTA pair per
-// 512x256 block (two row blocks sharing B).  The largest block the output's row count fills is used;
-// RZ_TC_CONFIG overrides it.
-int choose_config(const rz_problem *pb, int op)
-{
-    const uint32_t forced = env_u32("RZ_TC_CONFIG", 0);
-    if (forced >= 1 && forced <= 3) return (int)forced;
-    const int64_t rows = (op == RZ_OP_BACKWARD_WEIGHT) ? pb->K : pb->M;
-    const int64_t depth = (op == RZ_OP_FORWARD) ? pb->K : (op == RZ_OP_BACKWARD_INPUT ? pb->N : pb->M);
-    const int64_t stages = depth / (pb->precision == RZ_PREC_BF16 ? 64 : 32);
-    // With two row blocks every TMEM column is an accumulator, so the epilogue cannot overlap the next
-    // block's main loop; that only pays off when the contraction is long enough to amortise it.
-    if (rows >= 4 * TILE_R && stages >= 8 && pb->precision != RZ_PREC_FP32) return 3;
-    return rows >= 2 * TILE_R ? 2 : 1;
-}
-int config_ctas(int config) { return config == 1 ? 1 : 2; }
+// Block shape of a launch.  (ctas, rb, nc): CTAs per block (2 = cluster pair driving cta_group::2 MMAs), row
+// blocks per pair, block columns.  Blocks are rows = 128*ctas*rb by nc.
+struct TcConfig {
+    int ctas, rb, nc;
+};
 
-uint32_t dx_box_rows(const rz_problem *pb, int ctas)
+// Candidates from the largest block down, with the relative tensor throughput each sustains when the grid
+// fills the machine (the wide pair blocks move the fewest L2 bytes per flop; narrow single-CTA blocks are
+// L2-bound but keep every SM busy on small grids).
+const struct {
+    TcConfig cfg;
+    double speed;
+} kCandidates[] = {
+    {{2, 2, 256}, 1.00}, {{2, 1, 256}, 0.80}, {{1, 1, 256}, 0.58}, {{1, 1, 128}, 0.40}, {{1, 1, 64}, 0.25},
+};
+
+// Pick the block shape with the best (occupancy of the last wave) x (shape throughput), among the shapes the
+// problem allows.  RZ_TC_CONFIG = 1..5 forces candidate 5..1 in the order above (1 = 128x256 single CTA,
+// 2 = pair 256x256, 3 = pair 512x256, 4 = single 128x128, 5 = single 128x64).
+TcConfig choose_config(const rz_problem *pb, int op)
 {
-    const uint32_t bcols = (uint32_t)(TILE_C / ctas);
+    const bool bf16 = pb->precision == RZ_PREC_BF16;
+    const bool split = pb->precision == RZ_PREC_FP32;
+    const int64_t rows = (op == RZ_OP_BACKWARD_WEIGHT) ? pb->K : pb->M;
+    const int64_t cols = (op == RZ_OP_BACKWARD_INPUT) ? pb->K : pb->N;
+    const int64_t depth = (op == RZ_OP_FORWARD) ? pb->K : (op == RZ_OP_BACKWARD_INPUT ? pb->N : pb->M);
+    const int64_t stages = (depth + (bf16 ? 63 : 31)) / (bf16 ? 64 : 32);
+    const int sms = num_sms();
+    auto allowed = [&](const TcConfig &c) {
+        if (split && c.rb == 2) return false;                       // split precision has no two-row-block variant
+        // with two row blocks the epilogue cannot overlap the next main loop: the contraction must amortise it
+        // (the weight gradient's scatter epilogue is about three times as long as a store epilogue)
+        if (c.rb == 2 && stages < (op == RZ_OP_BACKWARD_WEIGHT ? 32 : 12)) return false;
+        const int64_t bcols = c.nc / c.ctas;                        // whole B boxes per hash tile (input gradient)
+        if (op == RZ_OP_BACKWARD_INPUT && (pb->BK <= bcols ? bcols % pb->BK != 0 : pb->BK % bcols != 0)) return false;
+        return true;
+    };
+    const uint32_t forced = env_u32("RZ_TC_CONFIG", 0);
+    if (forced >= 1 && forced <= 5) {
+        static const int order[5] = {2, 1, 0, 3, 4};
+        const TcConfig c = kCandidates[order[forced - 1]].cfg;
+        if (allowed(c)) return c;
+    }
+    TcConfig best = kCandidates[4].cfg;
+    double best_score = -1.0;
+    for (const auto &cand : kCandidates) {
+        const TcConfig &c = cand.cfg;
+        if (!allowed(c)) continue;
+        const int64_t block_rows = (int64_t)TILE_R * c.ctas * c.rb;
+        if (rows < block_rows / 2 && c.ctas * c.rb > 1) continue;   // do not pair CTAs over rows that do not exist
+        const int64_t items = ((rows + block_rows - 1) / block_rows) * ((cols + c.nc - 1) / c.nc);
+        const int64_t slots = sms / c.ctas;
+        const int64_t waves = (items + slots - 1) / slots;
+        const double occupancy = (double)items / (double)(waves * slots);
+        // useful fraction of the block (ragged last row block)
+        const double fill = (double)rows / (double)(((rows + block_rows - 1) / block_rows) * block_rows);
+        const double score = occupancy * fill * cand.speed;
+        if (score > best_score * 1.02) {   // prefer the larger block on near ties
+            best_score = score;
+            best = c;
+        }
+    }
+    return best;
+}
+
+uint32_t dx_box_rows(const rz_problem *pb, const TcConfig &c)
+{
+    const uint32_t bcols = (uint32_t)(c.nc / c.ctas);
     return (uint32_t)pb->BK < bcols ? (uint32_t)pb->BK : bcols;
 }
 
-template <int OP, bool TF32, int CTAS, int RB, int SPLIT>
+template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC>
 int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p)
 {
     const rz_problem *pb = c.pb;
@@ -763,14 +814,14 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.cols = (OP == OP_DX) ? p.K : p.N;
     const uint32_t depth = (OP == OP_FWD) ? p.K : (OP == OP_DX ? p.N : p.M);
     p.tiles_r = (p.rows + ITEM_R - 1) / ITEM_R;
-    p.tiles_c = (p.cols + TILE_C - 1) / TILE_C;
+    p.tiles_c = (p.cols + NC - 1) / NC;
     p.nchunks = (depth + KC - 1) / KC;
-    p.br = dx_box_rows(pb, CTAS);
+    p.br = dx_box_rows(pb, TcConfig{CTAS, RB, NC});
     p.group_rows = env_u32("RZ_TC_GROUP", GROUP_ROWS / RB);
     if (p.group_rows < 1) p.group_rows = 1;
 
-    auto kern = rz_tc_kernel<OP, TF32, CTAS, RB, SPLIT>;
-    constexpr int SMEM_TOTAL = smem_total(OP, CTAS, RB, SPLIT);
+    auto kern = rz_tc_kernel<OP, TF32, CTAS, RB, SPLIT, NC>;
+    constexpr int SMEM_TOTAL = smem_total(OP, CTAS, RB, SPLIT, NC);
     static_assert(SMEM_TOTAL <= SMEM_LIMIT, "shared memory budget");
     int st = rz_record_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL),
                             "set max dynamic shared memory");
@@ -837,7 +888,7 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     }
     const uint32_t a_major = (OP == OP_DW) ? 1u : 0u, b_major = (OP == OP_DX) ? 0u : 1u;
     const uint32_t fmt = TF32 ? 2u : 1u;
-    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (a_major << 15) | (b_major << 16) | ((uint32_t)(TILE_C >> 3) << 17) |
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (a_major << 15) | (b_major << 16) | ((uint32_t)(NC >> 3) << 17) |
               ((uint32_t)(PAIR_R >> 4) << 24);
 
     const uint32_t blocks = p.total_items < (uint32_t)slots ? p.total_items : (uint32_t)slots;
@@ -849,17 +900,25 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
 }
 
 template <int OP>
-int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, int config)
+int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, const TcConfig &cfg)
 {
     const int prec = c.pb->precision;
-    if (prec == RZ_PREC_FP32)   // split precision: fp32 operands, three tf32 MMAs per product
-        return config >= 2 ? launch_tc<OP, true, 2, 1, 1>(c, mapA, mapB, p) : launch_tc<OP, true, 1, 1, 1>(c, mapA, mapB, p);
+    if (prec == RZ_PREC_FP32) {   // split precision: fp32 operands, three tf32 MMAs per product
+        if (cfg.ctas == 2) return launch_tc<OP, true, 2, 1, 1, 256>(c, mapA, mapB, p);
+        if (cfg.nc == 256) return launch_tc<OP, true, 1, 1, 1, 256>(c, mapA, mapB, p);
+        if (cfg.nc == 128) return launch_tc<OP, true, 1, 1, 1, 128>(c, mapA, mapB, p);
+        return launch_tc<OP, true, 1, 1, 1, 64>(c, mapA, mapB, p);
+    }
     const bool tf32 = prec == RZ_PREC_TF32;
-    if (config == 3)
-        return tf32 ? launch_tc<OP, true, 2, 2, 0>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 2, 0>(c, mapA, mapB, p);
-    if (config == 2)
-        return tf32 ? launch_tc<OP, true, 2, 1, 0>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 1, 0>(c, mapA, mapB, p);
-    return tf32 ? launch_tc<OP, true, 1, 1, 0>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1, 0>(c, mapA, mapB, p);
+    if (cfg.ctas == 2 && cfg.rb == 2)
+        return tf32 ? launch_tc<OP, true, 2, 2, 0, 256>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 2, 0, 256>(c, mapA, mapB, p);
+    if (cfg.ctas == 2)
+        return tf32 ? launch_tc<OP, true, 2, 1, 0, 256>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 1, 0, 256>(c, mapA, mapB, p);
+    if (cfg.nc == 256)
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 256>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1, 0, 256>(c, mapA, mapB, p);
+    if (cfg.nc == 128)
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 128>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1, 0, 128>(c, mapA, mapB, p);
+    return tf32 ? launch_tc<OP, true, 1, 1, 0, 64>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1, 0, 64>(c, mapA, mapB, p);
 }
 
 // 2-D map over a row-major matrix [rows][cols] of the operand type
@@ -900,9 +959,9 @@ bool rz_tc_supported(const rz_problem *pb, int op)
     (void)op;
     const Geometry g = geometry(pb);
     if (pb->BK % g.epr || pb->BN % g.epr) return false;
-    if (pb->BK <= 128 ? (128 % pb->BK != 0) : (pb->BK % 128 != 0)) return false;  // whole B boxes per hash tile
+    if (pb->BK <= 64 ? (64 % pb->BK != 0) : (pb->BK % 64 != 0)) return false;   // whole B boxes per hash tile (narrowest block)
     if ((pb->K * g.es) % 16 || (pb->N * g.es) % 16) return false;
-    if (pb->M < TILE_R || pb->K < g.epr || pb->N < g.epr) return false;  // TMA boxes no larger than the matrices
+    if (pb->K < g.epr || pb->N < g.epr) return false;   // at least one full 128-byte row of every operand
     return true;
 }
 
@@ -965,8 +1024,8 @@ int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shado
     CUtensorMap mapA, mapB;
     int st = map_matrix(&mapA, tf32, false, dY, pb->M, pb->N, g.epr, TILE_R);
     if (st) return st;
-    const int config = choose_config(pb, RZ_OP_BACKWARD_INPUT);
-    st = map_shadow(&mapB, pb, false, shadow, dx_box_rows(pb, config_ctas(config)));
+    const TcConfig config = choose_config(pb, RZ_OP_BACKWARD_INPUT);
+    st = map_shadow(&mapB, pb, false, shadow, dx_box_rows(pb, config));
     if (st) return st;
     TcParams p;
     memset(&p, 0, sizeof(p));

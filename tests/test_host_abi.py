@@ -110,9 +110,10 @@ def test_null_pointers_are_rejected_before_any_launch(rzlib):
 
 def test_plan_selects_kernel_family(rzlib):
     # fp32 precision on fp32 data: tensor cores with split (hi/lo) operands when the shape is tile-aligned,
-    # FMA kernels otherwise (small batch, hash tile not a multiple of 32, forced)
+    # FMA kernels otherwise (hash tile not a multiple of 32, rows shorter than 128 bytes, forced)
     assert rzlib.plan(_pb(rzlib, M=1024, K=1024, N=1024, H=65536, BK=32, BN=32), 0) == rzlib.PATH_TCGEN05
-    assert rzlib.plan(_pb(rzlib, M=64, K=1024, N=1024, H=65536, BK=32, BN=32), 0) == rzlib.PATH_SIMT
+    assert rzlib.plan(_pb(rzlib, M=64, K=1024, N=1024, H=65536, BK=32, BN=32), 0) == rzlib.PATH_TCGEN05   # small batch too
+    assert rzlib.plan(_pb(rzlib, M=1024, K=16, N=1024, H=65536, BK=32, BN=32), 0) == rzlib.PATH_SIMT       # K below one 128-byte row
     assert rzlib.plan(_pb(rzlib, M=1024, K=1024, N=1024, H=65536, BK=16, BN=32), 0) == rzlib.PATH_SIMT
     assert rzlib.plan(_pb(rzlib, M=1024, K=1024, N=1024, H=65536, BK=32, BN=32, flags=rzlib.FLAG_FORCE_SIMT), 0) == rzlib.PATH_SIMT
     # tile-aligned bf16 / tf32 problems take the tensor-core kernels
@@ -127,4 +128,5 @@ def test_plan_selects_kernel_family(rzlib):
     # shadow scratch: NS shifted copies (8 for bf16, 4 for tf32), none for the FMA kernels
     assert rzlib.shadow_bytes(_pb(rzlib, io=1, prec=2, **big)) == 8 * (1 << 22) * 2
     assert rzlib.shadow_bytes(_pb(rzlib, io=0, prec=1, M=16384, K=4096, N=4096, H=1 << 20, BK=64, BN=64)) == 4 * (1 << 20) * 4
-    assert rzlib.shadow_bytes(_pb(rzlib)) == 0
+    assert rzlib.shadow_bytes(_pb(rzlib, flags=rzlib.FLAG_FORCE_SIMT)) == 0
+    assert rzlib.shadow_bytes(_pb(rzlib, BK=16)) == 0
