@@ -49,7 +49,8 @@ enum rz_hash_mode {
 enum rz_dtype { RZ_F32 = 0, RZ_BF16 = 1 };
 
 enum rz_precision {
-    RZ_PREC_FP32 = 0,  /* fp32 FMA arithmetic (reference: allow_tf32=False) */
+    RZ_PREC_FP32 = 0,  /* fp32-grade arithmetic (reference: allow_tf32=False): split tf32 operands on the
+                          tensor cores for fp32 data and tile-aligned shapes, fp32 FMA kernels otherwise */
     RZ_PREC_TF32 = 1,  /* tf32 tensor cores, fp32 accumulate (reference: allow_tf32=True); io fp32 */
     RZ_PREC_BF16 = 2   /* bf16 tensor cores, fp32 accumulate; io bf16, hashed array fp32 */
 };
@@ -93,8 +94,9 @@ int rz_plan(const rz_problem *pb, int op);
 
 /* Scratch ("shadow") memory the tensor-core forward / input-gradient kernels read instead of
    the fp32 hashed array: element-shifted copies in the compute type so that every tile slice
-   starts on a 16-byte boundary of one copy.  rz_shadow_bytes() is 0 when the problem takes the
-   SIMT path.  The caller allocates `shadow` (256-byte aligned), and refreshes it whenever
+   starts on a 16-byte boundary of one copy, followed (small batches, fp32 precision) by an fp32
+   workspace for partial sums of split contractions.  rz_shadow_bytes() is 0 when the problem takes
+   the SIMT path.  The caller allocates `shadow` (256-byte aligned), and refreshes it whenever
    `hashed` changes. */
 size_t rz_shadow_bytes(const rz_problem *pb);
 int rz_shadow_refresh(const rz_problem *pb, const float *hashed, void *shadow, void *stream);

@@ -96,6 +96,7 @@ struct TcParams {
     const float *bias;
     void *out;
     float *dH;
+    float *ws;                  // FWD / DX with a split contraction: fp32 partial sums [rows][cols]
     int *status;
     long long wait_limit;
 };
@@ -129,10 +130,17 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     static_assert(!SPLIT || (TF32 && RB == 1), "split precision: fp32 operands, one row block");
     constexpr int SMEM_RING = STAGES * STAGE_BYTES;
     constexpr int SMEM_EPI_OP = smem_epi(OP, RB);
-    constexpr int NBUF = 2 / RB;            // accumulator sets in TMEM (2: double-buffered, 1: none spare)
+    // accumulator sets in TMEM: 2 = double-buffered; 1 when both halves are in use by one block (two row blocks, or
+    // the main + correction accumulators of split precision)
+    constexpr int NBUF = (RB == 2 || SPLIT) ? 1 : 2;
     static_assert(STAGE_BYTES == stage_bytes(CTAS, RB, SPLIT, NC), "stage size");
     static_assert(NC == 256 || (CTAS == 1 && RB == 1), "narrow blocks: single CTA only");
     static_assert(2 * RB * NC <= 512 || RB == 2, "TMEM columns");
+    // Split precision keeps the hi*hi sums and the (2^-11 smaller) hi*lo + lo*hi corrections in separate accumulators:
+    // the tensor core truncates when it adds into an fp32 accumulator (about 2e-8 of the accumulator per MMA), so
+    // the corrections must not cost the main chain two more truncating adds per K-step.  Chains are further bounded
+    // by splitting long contractions on the host side.
+    constexpr int CORR_COL = NC;            // TMEM column offset of the correction accumulator (SPLIT only)
     static_assert(RB == 1 || CTAS == 2, "two row blocks only with CTA pairs");
     constexpr int A_ATOMS = TILE_R / EPR;
     constexpr int B_ATOMS = B_COLS / EPR;
@@ -342,11 +350,11 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                                 const uint64_t ad_lo = make_desc_sw128(sa + LOAD_BYTES + kk * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
                                 const uint64_t bd_lo = make_desc_sw128(sb + LOAD_BYTES + kk * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
                                 if (CTAS == 2) {
-                                    tc_mma_pair<TF32>(d_tmem, ad, bd_lo, p.idesc, 1u);
-                                    tc_mma_pair<TF32>(d_tmem, ad_lo, bd, p.idesc, 1u);
+                                    tc_mma_pair<TF32>(d_tmem + CORR_COL, ad, bd_lo, p.idesc, acc);
+                                    tc_mma_pair<TF32>(d_tmem + CORR_COL, ad_lo, bd, p.idesc, 1u);
                                 } else {
-                                    tc_mma<TF32>(d_tmem, ad, bd_lo, p.idesc, 1u);
-                                    tc_mma<TF32>(d_tmem, ad_lo, bd, p.idesc, 1u);
+                                    tc_mma<TF32>(d_tmem + CORR_COL, ad, bd_lo, p.idesc, acc);
+                                    tc_mma<TF32>(d_tmem + CORR_COL, ad_lo, bd, p.idesc, 1u);
                                 }
                             }
                         }
@@ -417,6 +425,13 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 }
                 tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + (buf * RB + rblk) * TILE_C + c * 32, v);
                 tmem_ld_wait();
+                if (SPLIT) {   // main + correction accumulators, added with round-to-nearest
+                    uint32_t w[32];
+                    tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + CORR_COL + c * 32, w);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+                }
                 const uint32_t col = tc * TILE_C + c * 32;
                 if (OP == OP_DW) {
                     float acc[32];
@@ -431,6 +446,12 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                         tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+                        if (SPLIT) {
+                            tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + CORR_COL + c2 * 32, v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+                        }
                         col_ok = col_ok || (tc * TILE_C + c2 * 32 + lane < p.N);
                     }
 #pragma unroll
@@ -444,6 +465,33 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                         const uint32_t nrow = min(32u, p.K - kb);
                         for (uint32_t rr = 0; rr < nrow; ++rr)
                             if (col_ok) atomicAdd(dst + (size_t)rr * (uint32_t)p.hash.BN, scratch[rr * 33 + lane]);
+                    }
+                    __syncwarp();
+                } else if (p.nsplit > 1) {
+                    // split contraction: add the raw fp32 partial sums into the workspace (a finalize kernel scales,
+                    // adds the bias and converts); staged like the store path so every reduction is a full row segment
+                    uint8_t *stage = reinterpret_cast<uint8_t *>(scratch);
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        uint4 u;
+                        u.x = v[4 * g + 0];
+                        u.y = v[4 * g + 1];
+                        u.z = v[4 * g + 2];
+                        u.w = v[4 * g + 3];
+                        *reinterpret_cast<uint4 *>(stage + lane * 128 + ((g ^ (lane & 7)) * 16)) = u;
+                    }
+                    __syncwarp();
+                    const uint32_t cc = lane & 7, ccol = col + cc * 4;
+#pragma unroll
+                    for (int it4 = 0; it4 < 8; ++it4) {
+                        const uint32_t rr = it4 * 4 + (lane >> 3);
+                        const uint4 u = *reinterpret_cast<const uint4 *>(stage + rr * 128 + ((cc ^ (rr & 7)) * 16));
+                        const uint32_t grow = rbase + rr;
+                        if (grow < p.rows && ccol < p.cols)
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.ws + (size_t)grow * p.cols + ccol),
+                                         "f"(__uint_as_float(u.x)), "f"(__uint_as_float(u.y)), "f"(__uint_as_float(u.z)),
+                                         "f"(__uint_as_float(u.w))
+                                         : "memory");
                     }
                     __syncwarp();
                 } else {
@@ -641,6 +689,32 @@ __global__ void rz_sgd_kernel(float *__restrict__ hashed, const float *__restric
     }
 }
 
+// out = convert(alpha * partial_sums (+ bias) (ReLU)) after a split-contraction FWD / DX launch
+template <typename T>
+__global__ void rz_finalize_kernel(const float *__restrict__ ws, T *__restrict__ out, const float *__restrict__ bias,
+                                   uint32_t rows, uint32_t cols, float alpha, int relu)
+{
+    const size_t n4 = (size_t)rows * cols / 4;   // cols is a multiple of 4
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 v = reinterpret_cast<const float4 *>(ws)[i];
+        v.x *= alpha, v.y *= alpha, v.z *= alpha, v.w *= alpha;
+        if (bias) {
+            const uint32_t c = (uint32_t)((i * 4) % cols);
+            v.x += bias[c], v.y += bias[c + 1], v.z += bias[c + 2], v.w += bias[c + 3];
+        }
+        if (relu) v.x = fmaxf(v.x, 0.f), v.y = fmaxf(v.y, 0.f), v.z = fmaxf(v.z, 0.f), v.w = fmaxf(v.w, 0.f);
+        if (sizeof(T) == 4) {
+            reinterpret_cast<float4 *>(out)[i] = v;
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            uint2 u;
+            u.x = *reinterpret_cast<uint32_t *>(&lo);
+            u.y = *reinterpret_cast<uint32_t *>(&hi);
+            reinterpret_cast<uint2 *>(out)[i] = u;
+        }
+    }
+}
+
 // ---- host side -----------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -729,6 +803,7 @@ uint32_t env_u32(const char *name, uint32_t dflt)
 // blocks per pair, block columns.  Blocks are rows = 128*ctas*rb by nc.
 struct TcConfig {
     int ctas, rb, nc;
+    int nsplit;   // parts the contraction is split into (1 = whole contraction per block)
 };
 
 // Candidates from the largest block down, with the relative tensor throughput each sustains when the grid
@@ -738,7 +813,7 @@ const struct {
     TcConfig cfg;
     double speed;
 } kCandidates[] = {
-    {{2, 2, 256}, 1.00}, {{2, 1, 256}, 0.80}, {{1, 1, 256}, 0.58}, {{1, 1, 128}, 0.40}, {{1, 1, 64}, 0.25},
+    {{2, 2, 256, 1}, 1.00}, {{2, 1, 256, 1}, 0.80}, {{1, 1, 256, 1}, 0.58}, {{1, 1, 128, 1}, 0.40}, {{1, 1, 64, 1}, 0.25},
 };
 
 // Pick the block shape with the best (occupancy of the last wave) x (shape throughput), among the shapes the
@@ -762,32 +837,61 @@ TcConfig choose_config(const rz_problem *pb, int op)
         if (op == RZ_OP_BACKWARD_INPUT && (pb->BK <= bcols ? bcols % pb->BK != 0 : pb->BK % bcols != 0)) return false;
         return true;
     };
+    // Small grids: split the contraction over several blocks so that every SM has work.  The weight gradient adds
+    // its partial blocks straight into the hashed gradient; FWD / DX add fp32 partials into a workspace that a
+    // finalize kernel scales and converts (two more small launches, so only contractions of 64 stages or more are
+    // split).  At least 16 pipeline stages per part.
+    auto split_for = [&](int64_t items, int64_t slots) {
+        if (items * 2 > slots) return (int64_t)1;
+        if (op != RZ_OP_BACKWARD_WEIGHT && stages < 64) return (int64_t)1;
+        int64_t want = slots / items, most = stages / (op == RZ_OP_BACKWARD_WEIGHT ? 8 : 16);
+        if (most < 1) most = 1;
+        return want < most ? want : most;
+    };
     const uint32_t forced = env_u32("RZ_TC_CONFIG", 0);
-    if (forced >= 1 && forced <= 5) {
-        static const int order[5] = {2, 1, 0, 3, 4};
-        const TcConfig c = kCandidates[order[forced - 1]].cfg;
-        if (allowed(c)) return c;
-    }
+    const bool no_split = env_u32("RZ_TC_NOSPLIT", 0) != 0;
     TcConfig best = kCandidates[4].cfg;
     double best_score = -1.0;
-    for (const auto &cand : kCandidates) {
-        const TcConfig &c = cand.cfg;
+    for (int i = 0; i < 5; ++i) {
+        const auto &cand = kCandidates[i];
+        TcConfig c = cand.cfg;
         if (!allowed(c)) continue;
         const int64_t block_rows = (int64_t)TILE_R * c.ctas * c.rb;
-        if (rows < block_rows / 2 && c.ctas * c.rb > 1) continue;   // do not pair CTAs over rows that do not exist
         const int64_t items = ((rows + block_rows - 1) / block_rows) * ((cols + c.nc - 1) / c.nc);
         const int64_t slots = sms / c.ctas;
-        const int64_t waves = (items + slots - 1) / slots;
-        const double occupancy = (double)items / (double)(waves * slots);
+        if (!no_split) c.nsplit = (int)split_for(items, slots);
+        if (split) {   // bound the accumulation chains of split precision: at most 2048 contraction elements per part
+            const int64_t need = (depth + 2047) / 2048;
+            if (c.nsplit < need) c.nsplit = (int)need;
+        }
+        if (forced >= 1 && forced <= 5) {
+            static const int order[5] = {2, 1, 0, 3, 4};
+            if (order[forced - 1] == i) return c;
+            continue;
+        }
+        if (rows < block_rows / 2 && c.ctas * c.rb > 1) continue;   // do not pair CTAs over rows that do not exist
+        const int64_t work = items * c.nsplit;
+        const int64_t waves = (work + slots - 1) / slots;
+        const double occupancy = (double)work / (double)(waves * slots);
         // useful fraction of the block (ragged last row block)
         const double fill = (double)rows / (double)(((rows + block_rows - 1) / block_rows) * block_rows);
-        const double score = occupancy * fill * cand.speed;
+        const double score = occupancy * fill * cand.speed * (c.nsplit > 1 ? 0.9 : 1.0);
         if (score > best_score * 1.02) {   // prefer the larger block on near ties
             best_score = score;
             best = c;
         }
     }
     return best;
+}
+
+// fp32 partial-sum workspace a split FWD / DX launch needs (0 for whole-contraction launches and for DW)
+size_t workspace_bytes(const rz_problem *pb, int op)
+{
+    if (op == RZ_OP_BACKWARD_WEIGHT) return 0;
+    const TcConfig c = choose_config(pb, op);
+    if (c.nsplit <= 1) return 0;
+    const size_t cols = (op == RZ_OP_BACKWARD_INPUT) ? (size_t)pb->K : (size_t)pb->N;
+    return ((size_t)pb->M * cols * sizeof(float) + 255) / 256 * 256;
 }
 
 uint32_t dx_box_rows(const rz_problem *pb, const TcConfig &c)
@@ -797,7 +901,7 @@ uint32_t dx_box_rows(const rz_problem *pb, const TcConfig &c)
 }
 
 template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC>
-int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p)
+int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, int nsplit_wanted)
 {
     const rz_problem *pb = c.pb;
     constexpr int ES = TF32 ? 4 : 2;
@@ -851,14 +955,9 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     }
 
     const uint32_t tiles = p.tiles_r * p.tiles_c;
-    p.nsplit = 1;
-    if (OP == OP_DW && tiles < (uint32_t)slots) {
-        // split the batch so that every SM gets work; each split adds into dH independently
-        uint32_t want = ((uint32_t)slots + tiles - 1) / tiles;
-        uint32_t max_split = (p.nchunks + 7) / 8;  // at least 8 stages per split
-        if (max_split < 1) max_split = 1;
-        p.nsplit = want < max_split ? want : max_split;
-    }
+    p.nsplit = nsplit_wanted > 1 ? (uint32_t)nsplit_wanted : 1u;
+    if (OP != OP_DW && !p.ws) p.nsplit = 1;   // no workspace given: whole contraction per block
+    if (p.nsplit > p.nchunks) p.nsplit = p.nchunks;
     p.chunks_per_split = (p.nchunks + p.nsplit - 1) / p.nsplit;
     p.nsplit = (p.nchunks + p.chunks_per_split - 1) / p.chunks_per_split;
     p.total_items = tiles * p.nsplit;
@@ -893,10 +992,28 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
 
     const uint32_t blocks = p.total_items < (uint32_t)slots ? p.total_items : (uint32_t)slots;
     cfg.gridDim = dim3(blocks * CTAS, 1, 1);
+    const bool partial = OP != OP_DW && p.nsplit > 1;
+    if (partial) {
+        st = rz_record_cuda(cudaMemsetAsync(p.ws, 0, sizeof(float) * (size_t)p.rows * p.cols, c.stream), "zero workspace");
+        if (st) return st;
+    }
     st = rz_record_cuda(cudaLaunchKernelEx(&cfg, kern, mapA, mapB, p), "tcgen05 kernel launch");
     rz_count_launch(1);
     if (st) return st;
-    return rz_record_cuda(cudaGetLastError(), "tcgen05 kernel launch");
+    st = rz_record_cuda(cudaGetLastError(), "tcgen05 kernel launch");
+    if (st || !partial) return st;
+    const size_t n4 = (size_t)p.rows * p.cols / 4;
+    unsigned fblocks = (unsigned)((n4 + 255) / 256);
+    if (fblocks > 148u * 8u) fblocks = 148u * 8u;
+    const float *fbias = OP == OP_FWD ? p.bias : nullptr;   // bias and ReLU belong to the forward pass only
+    const int frelu = OP == OP_FWD ? p.relu : 0;
+    if (TF32)
+        rz_finalize_kernel<float><<<fblocks, 256, 0, c.stream>>>(p.ws, (float *)p.out, fbias, p.rows, p.cols, p.alpha, frelu);
+    else
+        rz_finalize_kernel<__nv_bfloat16><<<fblocks, 256, 0, c.stream>>>(p.ws, (__nv_bfloat16 *)p.out, fbias, p.rows, p.cols,
+                                                                          p.alpha, frelu);
+    rz_count_launch(1);
+    return rz_record_cuda(cudaGetLastError(), "finalize launch");
 }
 
 template <int OP>
@@ -904,21 +1021,21 @@ int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorM
 {
     const int prec = c.pb->precision;
     if (prec == RZ_PREC_FP32) {   // split precision: fp32 operands, three tf32 MMAs per product
-        if (cfg.ctas == 2) return launch_tc<OP, true, 2, 1, 1, 256>(c, mapA, mapB, p);
-        if (cfg.nc == 256) return launch_tc<OP, true, 1, 1, 1, 256>(c, mapA, mapB, p);
-        if (cfg.nc == 128) return launch_tc<OP, true, 1, 1, 1, 128>(c, mapA, mapB, p);
-        return launch_tc<OP, true, 1, 1, 1, 64>(c, mapA, mapB, p);
+        if (cfg.ctas == 2) return launch_tc<OP, true, 2, 1, 1, 256>(c, mapA, mapB, p, cfg.nsplit);
+        if (cfg.nc == 256) return launch_tc<OP, true, 1, 1, 1, 256>(c, mapA, mapB, p, cfg.nsplit);
+        if (cfg.nc == 128) return launch_tc<OP, true, 1, 1, 1, 128>(c, mapA, mapB, p, cfg.nsplit);
+        return launch_tc<OP, true, 1, 1, 1, 64>(c, mapA, mapB, p, cfg.nsplit);
     }
     const bool tf32 = prec == RZ_PREC_TF32;
     if (cfg.ctas == 2 && cfg.rb == 2)
-        return tf32 ? launch_tc<OP, true, 2, 2, 0, 256>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 2, 0, 256>(c, mapA, mapB, p);
+        return tf32 ? launch_tc<OP, true, 2, 2, 0, 256>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 2, 2, 0, 256>(c, mapA, mapB, p, cfg.nsplit);
     if (cfg.ctas == 2)
-        return tf32 ? launch_tc<OP, true, 2, 1, 0, 256>(c, mapA, mapB, p) : launch_tc<OP, false, 2, 1, 0, 256>(c, mapA, mapB, p);
+        return tf32 ? launch_tc<OP, true, 2, 1, 0, 256>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 2, 1, 0, 256>(c, mapA, mapB, p, cfg.nsplit);
     if (cfg.nc == 256)
-        return tf32 ? launch_tc<OP, true, 1, 1, 0, 256>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1, 0, 256>(c, mapA, mapB, p);
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 256>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 1, 1, 0, 256>(c, mapA, mapB, p, cfg.nsplit);
     if (cfg.nc == 128)
-        return tf32 ? launch_tc<OP, true, 1, 1, 0, 128>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1, 0, 128>(c, mapA, mapB, p);
-    return tf32 ? launch_tc<OP, true, 1, 1, 0, 64>(c, mapA, mapB, p) : launch_tc<OP, false, 1, 1, 0, 64>(c, mapA, mapB, p);
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 128>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 1, 1, 0, 128>(c, mapA, mapB, p, cfg.nsplit);
+    return tf32 ? launch_tc<OP, true, 1, 1, 0, 64>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 1, 1, 0, 64>(c, mapA, mapB, p, cfg.nsplit);
 }
 
 // 2-D map over a row-major matrix [rows][cols] of the operand type
@@ -967,8 +1084,17 @@ bool rz_tc_supported(const rz_problem *pb, int op)
 
 size_t rz_tc_shadow_bytes(const rz_problem *pb)
 {
+    // the shifted copies, then the fp32 workspace of split-contraction launches (forward and input gradient share it)
     const Geometry g = geometry(pb);
-    return g.copy_stride * (size_t)g.ns;
+    const size_t wf = workspace_bytes(pb, RZ_OP_FORWARD), wi = workspace_bytes(pb, RZ_OP_BACKWARD_INPUT);
+    return g.copy_stride * (size_t)g.ns + (wf > wi ? wf : wi);
+}
+
+static float *workspace_of(const rz_problem *pb, const void *shadow, int op)
+{
+    if (workspace_bytes(pb, op) == 0) return nullptr;
+    const Geometry g = geometry(pb);
+    return reinterpret_cast<float *>(const_cast<uint8_t *>(static_cast<const uint8_t *>(shadow)) + g.copy_stride * (size_t)g.ns);
 }
 
 int rz_tc_shadow_refresh(const RzLaunchCtx &c, const float *hashed, void *shadow)
@@ -1013,6 +1139,7 @@ int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const
     memset(&p, 0, sizeof(p));
     p.bias = bias;
     p.out = Y;
+    p.ws = workspace_of(pb, shadow, RZ_OP_FORWARD);
     return launch_tc_any<OP_FWD>(c, mapA, mapB, p, choose_config(pb, RZ_OP_FORWARD));
 }
 
@@ -1030,6 +1157,7 @@ int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shado
     TcParams p;
     memset(&p, 0, sizeof(p));
     p.out = dX;
+    p.ws = workspace_of(pb, shadow, RZ_OP_BACKWARD_INPUT);
     return launch_tc_any<OP_DX>(c, mapA, mapB, p, config);
 }
 

@@ -19,7 +19,7 @@ def one_case(rzlib, rs, prec):
     bf16 = prec == rzlib.PREC_BF16
     unit = 8 if bf16 else 4                      # leading dimensions in multiples of 16 bytes
     tile_unit = 64 if bf16 else 32
-    M = int(rs.choice([128, 136, 200, 256, 384, 520, 640, 1024, 1500]))
+    M = int(rs.choice([8, 32, 72, 128, 136, 200, 256, 384, 520, 640, 1024, 1500]))
     K = int(rs.randint(tile_unit // unit, 96)) * unit
     N = int(rs.randint(tile_unit // unit, 96)) * unit
     BK = int(rs.choice([tile_unit, 2 * tile_unit, 128, 256]))
@@ -95,3 +95,47 @@ def test_configs_forced(rzlib, monkeypatch):
             errs, desc = one_case(rzlib, rs2, rzlib.PREC_BF16)
         assert max(errs) < 2e-3, (config, errs, desc)
     monkeypatch.delenv("RZ_TC_CONFIG")
+
+
+@pytest.mark.parametrize("prec_name,tol", [("bf16", 2e-3), ("tf32", 2e-3), ("fp32", 1e-5)])
+@pytest.mark.parametrize("M,K,N", [(32, 4096, 4096), (128, 4096, 2560), (8, 8192, 4096), (256, 8192, 4096)])
+def test_split_contraction_small_batches(rzlib, prec_name, tol, M, K, N):
+    # few output blocks and a long contraction: the contraction is split over CTAs, fp32 partial sums go
+    # through the workspace that rz_shadow_bytes() adds to the scratch, a finalize kernel scales/biases/converts
+    prec = {"bf16": rzlib.PREC_BF16, "tf32": rzlib.PREC_TF32, "fp32": rzlib.PREC_FP32}[prec_name]
+    bf16 = prec == rzlib.PREC_BF16
+    dtype = torch.bfloat16 if bf16 else torch.float32
+    io = rzlib.BF16 if bf16 else rzlib.F32
+    H, BK, BN = 300007, 64, 64
+    R = [PRIME] + [int(v) for v in np.random.RandomState(M + K).randint(1, 2**31 - 1, 7)]
+    g = torch.Generator(device=DEV).manual_seed(M * 7 + N)
+    X = torch.randn((M, K), generator=g, device=DEV).to(dtype)
+    dY = torch.randn((M, N), generator=g, device=DEV).to(dtype)
+    h = (torch.rand(H, generator=g, device=DEV) * 2 - 1) / K ** 0.5
+    bias = torch.randn(N, generator=g, device=DEV)
+    pb = rzlib.make_problem(M, K, N, H, BK, BN, R, 0, io, prec, 0.5, rzlib.FLAG_RELU)
+    ref = rzlib.make_problem(M, K, N, H, BK, BN, R, 0, io, prec, 0.5, rzlib.FLAG_RELU | rzlib.FLAG_FORCE_SIMT)
+    assert rzlib.plan(pb, 0) == rzlib.PATH_TCGEN05
+    copies = (16 // (2 if bf16 else 4)) * (-(-H // 64) * 64) * (2 if bf16 else 4)
+    assert rzlib.shadow_bytes(pb) > copies          # the workspace is part of the scratch for these shapes
+    nbytes = rzlib.shadow_bytes(pb)
+    shadow = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+    rzlib.shadow_refresh(pb, h, shadow)
+    Y = torch.empty((M, N), dtype=dtype, device=DEV)
+    dX = torch.empty((M, K), dtype=dtype, device=DEV)
+    dH = torch.empty(H, dtype=torch.float32, device=DEV)
+    rzlib.forward(pb, X, h, shadow, bias, Y)
+    rzlib.backward_input(pb, dY, h, shadow, dX)
+    rzlib.backward_weight(pb, X, dY, dH)
+    dH_ref = torch.empty(H, dtype=torch.float32, device=DEV)
+    rzlib.backward_weight(ref, X, dY, dH_ref)          # short contraction (M rows): the FMA kernels are exact enough
+    torch.cuda.synchronize()
+    assert rzlib.device_status() == (0, 0)
+    # long contractions: fp64 matmul over the materialised weight (bit-exact gather) is the reference
+    from rzlinear_b200.impl.launchers import rz_linear_idx_tl
+    hw = h.bfloat16().float() if bf16 else h
+    W = rz_linear_idx_tl(hw, K, N, H, R[3], R[2], R[1], R[0], BK, BN).double()
+    Y_ref = torch.relu(0.5 * (X.double() @ W) + bias.double())
+    dX_ref = 0.5 * (dY.double() @ W.t())
+    errs = (rel(Y.float(), Y_ref), rel(dX.float(), dX_ref), rel(dH, dH_ref))
+    assert max(errs) < tol, errs
