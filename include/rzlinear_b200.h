@@ -141,6 +141,11 @@ int rz_linear_materialize(const rz_problem *pb, const float *hashed, float *W, v
 int rz_sgd_step(const rz_problem *pb, float *hashed, const float *dH, float lr, void *shadow,
                 void *stream);
 
+/* Heavy-ball variant: velocity = momentum * velocity + dH; hashed -= lr * velocity (velocity fp32 [H], caller-owned);
+   the shadow copies are rewritten afterwards when shadow != NULL.  No counterpart in the reference. */
+int rz_sgd_momentum_step(const rz_problem *pb, float *hashed, const float *dH, float *velocity, float lr,
+                         float momentum, void *shadow, void *stream);
+
 /* Reads and clears the device-side status word (synchronises the device).  *out = RZ_OK or
    RZ_ERR_PIPELINE; *detail (may be NULL) receives the code of the wait that gave up. */
 int rz_device_status(int *out, int *detail);

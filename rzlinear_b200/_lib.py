@@ -28,7 +28,7 @@ EXPORTS = [
     "rz_hash_indices_device", "rz_plan", "rz_shadow_bytes", "rz_shadow_refresh",
     "rz_linear_forward", "rz_linear_backward_input", "rz_linear_backward_weight",
     "rz_linear_materialize", "rz_sgd_step", "rz_device_status", "rz_launch_count",
-    "rz_selftest_bounded_wait",
+    "rz_selftest_bounded_wait", "rz_sgd_momentum_step",
 ]
 
 
@@ -205,6 +205,17 @@ def sgd_step(pb, hashed, dh, lr, shadow) -> None:
     with torch.cuda.device(hashed.device):
         check(load().rz_sgd_step(ctypes.byref(pb), _ptr(hashed), _ptr(dh), ctypes.c_float(lr), _ptr(shadow),
                                  _stream(hashed.device)))
+
+
+def sgd_momentum_step(pb, hashed, dh, velocity, lr, momentum, shadow) -> None:
+    _require_cuda(hashed, dh, velocity, shadow)
+    fn = load().rz_sgd_momentum_step
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.POINTER(RzProblem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
+                   ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]
+    with torch.cuda.device(hashed.device):
+        check(fn(ctypes.byref(pb), _ptr(hashed), _ptr(dh), _ptr(velocity), ctypes.c_float(lr), ctypes.c_float(momentum),
+                 _ptr(shadow), _stream(hashed.device)))
 
 
 def device_status():

@@ -225,6 +225,18 @@ int rz_sgd_step(const rz_problem *pb, float *hashed, const float *dH, float lr, 
     return rz_tc_sgd_step(make_ctx(pb, stream), hashed, dH, lr, shadow);
 }
 
+int rz_sgd_momentum_step(const rz_problem *pb, float *hashed, const float *dH, float *velocity, float lr, float momentum,
+                         void *shadow, void *stream)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!hashed || !dH || !velocity) return RZ_ERR_NULL;
+    if (!aligned16(hashed) || !aligned16(dH) || !aligned16(velocity)) return RZ_ERR_ALIGN;
+    if (shadow && rz_shadow_bytes(pb) == 0) shadow = nullptr;
+    if (shadow && (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
+    return rz_tc_sgd_momentum_step(make_ctx(pb, stream), hashed, dH, velocity, lr, momentum, shadow);
+}
+
 int rz_device_status(int *out, int *detail)
 {
     if (!out) return RZ_ERR_NULL;

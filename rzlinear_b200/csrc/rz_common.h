@@ -41,6 +41,8 @@ bool rz_tc_supported(const rz_problem *pb, int op);
 size_t rz_tc_shadow_bytes(const rz_problem *pb);
 int rz_tc_shadow_refresh(const RzLaunchCtx &c, const float *hashed, void *shadow);
 int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float lr, void *shadow);
+int rz_tc_sgd_momentum_step(const RzLaunchCtx &c, float *hashed, const float *dH, float *velocity, float lr, float momentum,
+                            void *shadow);
 int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const float *bias, void *Y);
 int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shadow, void *dX);
 int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, float *dH);

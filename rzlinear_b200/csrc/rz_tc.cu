@@ -689,6 +689,17 @@ __global__ void rz_sgd_kernel(float *__restrict__ hashed, const float *__restric
     }
 }
 
+// v = momentum * v + dH;  hashed -= lr * v   (heavy-ball SGD on the hashed array)
+__global__ void rz_sgd_momentum_kernel(float *__restrict__ hashed, const float *__restrict__ dH, float *__restrict__ vel,
+                                       float lr, float momentum, uint32_t H)
+{
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) {
+        const float v = momentum * vel[i] + dH[i];
+        vel[i] = v;
+        hashed[i] -= lr * v;
+    }
+}
+
 // out = convert(alpha * partial_sums (+ bias) (ReLU)) after a split-contraction FWD / DX launch
 template <typename T>
 __global__ void rz_finalize_kernel(const float *__restrict__ ws, T *__restrict__ out, const float *__restrict__ bias,
@@ -817,7 +828,7 @@ const struct {
 };
 
 // Pick the block shape with the best (occupancy of the last wave) x (shape throughput), among the shapes the
-// problem allows.  RZ_TC_CONFIG = 1..5 forces candidate 5..1 in the order above (1 = 128x256 single CTA,
+// problem allows.  RZ_TC_CONFIG = 1..5 forces one shape (1 = 128x256 single CTA,
 // 2 = pair 256x256, 3 = pair 512x256, 4 = single 128x128, 5 = single 128x64).
 TcConfig choose_config(const rz_problem *pb, int op)
 {
@@ -1121,6 +1132,19 @@ int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float l
     rz_sgd_kernel<<<blocks, 256, 0, c.stream>>>(hashed, dH, lr, H);
     rz_count_launch(1);
     int st = rz_record_cuda(cudaGetLastError(), "sgd launch");
+    if (st || !shadow) return st;
+    return rz_tc_shadow_refresh(c, hashed, shadow);
+}
+
+int rz_tc_sgd_momentum_step(const RzLaunchCtx &c, float *hashed, const float *dH, float *velocity, float lr, float momentum,
+                            void *shadow)
+{
+    const uint32_t H = (uint32_t)c.pb->H;
+    uint32_t blocks = (H + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    rz_sgd_momentum_kernel<<<blocks, 256, 0, c.stream>>>(hashed, dH, velocity, lr, momentum, H);
+    rz_count_launch(1);
+    int st = rz_record_cuda(cudaGetLastError(), "sgd momentum launch");
     if (st || !shadow) return st;
     return rz_tc_shadow_refresh(c, hashed, shadow);
 }

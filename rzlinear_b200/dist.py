@@ -41,8 +41,11 @@ class CudaKernels:
     def backward_weight(self, x, dy, dh):
         _lib.backward_weight(self.pb, x, dy, dh)
 
-    def sgd(self, hashed, dh, lr):
-        _lib.sgd_step(self.pb, hashed, dh, lr, self.shadow)
+    def sgd(self, hashed, dh, lr, velocity=None, momentum=0.0):
+        if velocity is None:
+            _lib.sgd_step(self.pb, hashed, dh, lr, self.shadow)
+        else:
+            _lib.sgd_momentum_step(self.pb, hashed, dh, velocity, lr, momentum, self.shadow)
 
 
 def shard_rows(M_global: int, rank: int, world: int):
@@ -56,11 +59,12 @@ class RzDataParallelStep:
     def __init__(self, M_local: int, K: int, N: int, H: int, BK: int, BN: int, R: Sequence[int],
                  hash_mode: int = _lib.HASH_SINGLE, dtype: torch.dtype = torch.bfloat16, lr: float = 1e-3,
                  device="cuda", init_factor: float = 1.0, allow_tf32: bool = True,
-                 process_group: Optional[dist.ProcessGroup] = None, kernels=None):
+                 process_group: Optional[dist.ProcessGroup] = None, kernels=None, momentum: float = 0.0):
         self.M, self.K, self.N, self.H = M_local, K, N, H
         self.device = torch.device(device)
         self.dtype = dtype
         self.lr = float(lr)
+        self.momentum = float(momentum)
         self.group = process_group
         self.world = dist.get_world_size(process_group) if (dist.is_available() and dist.is_initialized()) else 1
         prec = _lib.PREC_BF16 if dtype == torch.bfloat16 else (_lib.PREC_TF32 if allow_tf32 else _lib.PREC_FP32)
@@ -69,6 +73,7 @@ class RzDataParallelStep:
         self.kernels = kernels if kernels is not None else CudaKernels(self.pb, self.device)
         self.hashed = torch.zeros(H, dtype=torch.float32, device=self.device)
         self.dH = torch.empty(H, dtype=torch.float32, device=self.device)
+        self.velocity = torch.zeros(H, dtype=torch.float32, device=self.device) if self.momentum != 0.0 else None
         self.Y = torch.empty((M_local, N), dtype=dtype, device=self.device)
         self.dX = torch.empty((M_local, K), dtype=dtype, device=self.device)
         self._pipe = None
@@ -76,6 +81,12 @@ class RzDataParallelStep:
     def load_weights(self, hashed: torch.Tensor) -> None:
         self.hashed.copy_(hashed.to(self.hashed.dtype), non_blocking=True)
         self.kernels.refresh(self.hashed)
+
+    def _update(self) -> None:
+        if self.velocity is None:
+            self.kernels.sgd(self.hashed, self.dH, self.lr)
+        else:
+            self.kernels.sgd(self.hashed, self.dH, self.lr, self.velocity, self.momentum)
 
     def step(self, X: torch.Tensor, dY: torch.Tensor, marks=None) -> None:
         """One training step on device-resident shards; results in self.Y, self.dX, self.dH, self.hashed.
@@ -95,7 +106,7 @@ class RzDataParallelStep:
         mark("backward_input")
         if work is not None:
             work.wait()
-        k.sgd(self.hashed, self.dH, self.lr)
+        self._update()
         mark("sgd")
 
     def _host_pipeline(self, chunk_rows: int):
@@ -158,5 +169,5 @@ class RzDataParallelStep:
             pipe["consumed"][i] = ev
         if work is not None:
             work.wait()
-        self.kernels.sgd(self.hashed, self.dH, self.lr)
+        self._update()
         hashed_out_host.copy_(self.hashed, non_blocking=True)

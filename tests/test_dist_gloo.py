@@ -30,7 +30,10 @@ class OracleKernels:
     def backward_weight(self, x, dy, dh):
         dh.copy_(torch.from_numpy(o.backward_weight(x.numpy(), dy.numpy(), H, BK, BN, R, 0)).to(dh.dtype))
 
-    def sgd(self, hashed, dh, lr):
+    def sgd(self, hashed, dh, lr, velocity=None, momentum=0.0):
+        if velocity is not None:
+            velocity.mul_(momentum).add_(dh)
+            dh = velocity
         hashed.sub_(lr * dh)
 
 

@@ -55,6 +55,22 @@ def test_single_rank_step_matches_oracle(rzlib):
     assert o.rel_l2(step.Y.float().cpu().numpy(), Y2) < 2e-3
 
 
+def test_momentum_update_matches_reference(rzlib):
+    from rzlinear_b200.dist import RzDataParallelStep
+    X, dY, h = _inputs()
+    step = RzDataParallelStep(M, K, N, H, BK, BN, R, rzlib.HASH_SINGLE, torch.bfloat16, LR, "cuda:0", momentum=0.9)
+    step.load_weights(h.cuda())
+    dH = _expected()[2]
+    hh, v = h.numpy().astype(np.float64), np.zeros(H)
+    for _ in range(2):      # dY is given, so the hashed-weight gradient is the same in both steps
+        step.step(X.cuda(), dY.cuda())
+        v = 0.9 * v + dH
+        hh = hh - LR * v
+    torch.cuda.synchronize()
+    assert o.rel_l2(step.velocity.cpu().numpy(), v) < 2e-3
+    assert o.rel_l2(step.hashed.cpu().numpy(), hh) < 1e-5
+
+
 def test_step_from_host_buffers(rzlib):
     from rzlinear_b200.dist import RzDataParallelStep
     X, dY, h = _inputs()
