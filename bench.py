@@ -175,6 +175,11 @@ def main():
         return
 
     import torch.distributed as dist
+    if world == 1:
+        # a source-only checkout: build the CUDA library in-tree first (no fallback exists if that fails)
+        from rzlinear_b200 import build as rzbuild
+        if not os.path.exists(rzbuild.LIB_PATH):
+            rzbuild.build()
     from rzlinear_b200 import _lib
     from rzlinear_b200.dist import RzDataParallelStep, shard_rows
 
