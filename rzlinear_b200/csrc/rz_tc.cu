@@ -84,7 +84,8 @@ struct TcParams {
     uint32_t rows, cols;        // output extents (elements)
     uint32_t tiles_r, tiles_c;
     uint32_t nchunks;           // pipeline stages along the whole contraction
-    uint32_t nsplit, chunks_per_split;
+    uint32_t nsplit, chunks_per_split;   // blocks from index n_main on are split into nsplit parts of the contraction
+    uint32_t n_main;                      // blocks [0, n_main) run their whole contraction in one work item
     uint32_t total_items;
     uint32_t br;                // OP_DX: slice rows per B box
     uint32_t group_rows;        // row tiles per rasterisation group
@@ -202,17 +203,29 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
 
     bool ok = true;
 
-    // decode a work item into its output block and contraction range
+    // decode a work item into its output block and contraction range; `tile` is the block index in rasterisation
+    // order, `partial` says that the item is one of several parts of its block's contraction
+    uint32_t tile = 0;
+    bool partial = false;
     auto decode = [&](uint32_t item, uint32_t &tr, uint32_t &tc, uint32_t &c_begin, uint32_t &c_end) {
-        uint32_t tile = item / p.nsplit, split = item - tile * p.nsplit;
+        uint32_t split = 0;
+        if (item < p.n_main) {
+            tile = item;
+            partial = false;
+        } else {
+            const uint32_t idx = item - p.n_main, q = idx / p.nsplit;
+            tile = p.n_main + q;
+            split = idx - q * p.nsplit;
+            partial = p.nsplit > 1;
+        }
         uint32_t per_group = p.group_rows * p.tiles_c;
         uint32_t group = tile / per_group, within = tile - group * per_group;
         uint32_t first_r = group * p.group_rows;
         uint32_t gsz = min(p.tiles_r - first_r, p.group_rows);
         tr = first_r + within % gsz;
         tc = within / gsz;
-        c_begin = split * p.chunks_per_split;
-        c_end = min(p.nchunks, c_begin + p.chunks_per_split);
+        c_begin = partial ? split * p.chunks_per_split : 0u;
+        c_end = partial ? min(p.nchunks, c_begin + p.chunks_per_split) : p.nchunks;
     };
 
     if (warp == 0) {
@@ -467,9 +480,10 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                             if (col_ok) atomicAdd(dst + (size_t)rr * (uint32_t)p.hash.BN, scratch[rr * 33 + lane]);
                     }
                     __syncwarp();
-                } else if (p.nsplit > 1) {
-                    // split contraction: add the raw fp32 partial sums into the workspace (a finalize kernel scales,
-                    // adds the bias and converts); staged like the store path so every reduction is a full row segment
+                } else if (partial) {
+                    // split contraction: add the raw fp32 partial sums into this block's ITEM_R x NC workspace tile (a
+                    // finalize kernel scales, adds the bias and converts); staged like the store path so every
+                    // reduction is a full row segment
                     uint8_t *stage = reinterpret_cast<uint8_t *>(scratch);
 #pragma unroll
                     for (int g = 0; g < 8; ++g) {
@@ -482,13 +496,15 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     }
                     __syncwarp();
                     const uint32_t cc = lane & 7, ccol = col + cc * 4;
+                    float *wtile = p.ws + (size_t)(tile - p.n_main) * (ITEM_R * NC) +
+                                   (size_t)(rbase - tr * ITEM_R) * NC + (c * 32 + cc * 4);
 #pragma unroll
                     for (int it4 = 0; it4 < 8; ++it4) {
                         const uint32_t rr = it4 * 4 + (lane >> 3);
                         const uint4 u = *reinterpret_cast<const uint4 *>(stage + rr * 128 + ((cc ^ (rr & 7)) * 16));
                         const uint32_t grow = rbase + rr;
                         if (grow < p.rows && ccol < p.cols)
-                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.ws + (size_t)grow * p.cols + ccol),
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(wtile + (size_t)rr * NC),
                                          "f"(__uint_as_float(u.x)), "f"(__uint_as_float(u.y)), "f"(__uint_as_float(u.z)),
                                          "f"(__uint_as_float(u.w))
                                          : "memory");
@@ -700,28 +716,45 @@ __global__ void rz_sgd_momentum_kernel(float *__restrict__ hashed, const float *
     }
 }
 
-// out = convert(alpha * partial_sums (+ bias) (ReLU)) after a split-contraction FWD / DX launch
+// out = convert(alpha * partial_sums (+ bias) (ReLU)) for the blocks of a FWD / DX launch whose contraction was
+// split: block n_main + i owns workspace tile i (item_r x nc floats, row-major); gridDim.y CTAs share a block.
+struct FinalizeGeom {
+    uint32_t rows, cols, item_r, nc, tiles_r, tiles_c, group_rows, n_main, n_tiles;
+};
+
 template <typename T>
 __global__ void rz_finalize_kernel(const float *__restrict__ ws, T *__restrict__ out, const float *__restrict__ bias,
-                                   uint32_t rows, uint32_t cols, float alpha, int relu)
+                                   FinalizeGeom g, float alpha, int relu)
 {
-    const size_t n4 = (size_t)rows * cols / 4;   // cols is a multiple of 4
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
-        float4 v = reinterpret_cast<const float4 *>(ws)[i];
-        v.x *= alpha, v.y *= alpha, v.z *= alpha, v.w *= alpha;
-        if (bias) {
-            const uint32_t c = (uint32_t)((i * 4) % cols);
-            v.x += bias[c], v.y += bias[c + 1], v.z += bias[c + 2], v.w += bias[c + 3];
-        }
-        if (relu) v.x = fmaxf(v.x, 0.f), v.y = fmaxf(v.y, 0.f), v.z = fmaxf(v.z, 0.f), v.w = fmaxf(v.w, 0.f);
-        if (sizeof(T) == 4) {
-            reinterpret_cast<float4 *>(out)[i] = v;
-        } else {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-            uint2 u;
-            u.x = *reinterpret_cast<uint32_t *>(&lo);
-            u.y = *reinterpret_cast<uint32_t *>(&hi);
-            reinterpret_cast<uint2 *>(out)[i] = u;
+    const uint32_t quads_per_row = g.nc / 4;
+    for (uint32_t i = blockIdx.x; i + g.n_main < g.n_tiles; i += gridDim.x) {
+        const uint32_t tile = g.n_main + i;
+        const uint32_t per_group = g.group_rows * g.tiles_c;
+        const uint32_t group = tile / per_group, within = tile - group * per_group;
+        const uint32_t first_r = group * g.group_rows;
+        const uint32_t gsz = min(g.tiles_r - first_r, g.group_rows);
+        const uint32_t tr = first_r + within % gsz, tc = within / gsz;
+        const float *wt = ws + (size_t)i * g.item_r * g.nc;
+        const uint32_t valid_rows = min(g.item_r, g.rows - tr * g.item_r);   // rows of the block that exist
+        const uint32_t nq = valid_rows * quads_per_row;
+        for (uint32_t e = blockIdx.y * blockDim.x + threadIdx.x; e < nq; e += blockDim.x * gridDim.y) {
+            const uint32_t lr = e / quads_per_row, lc = (e - lr * quads_per_row) * 4;
+            const uint32_t row = tr * g.item_r + lr, col = tc * g.nc + lc;
+            if (row >= g.rows || col >= g.cols) continue;   // cols is a multiple of 4
+            float4 v = *reinterpret_cast<const float4 *>(wt + (size_t)lr * g.nc + lc);
+            v.x *= alpha, v.y *= alpha, v.z *= alpha, v.w *= alpha;
+            if (bias) v.x += bias[col], v.y += bias[col + 1], v.z += bias[col + 2], v.w += bias[col + 3];
+            if (relu) v.x = fmaxf(v.x, 0.f), v.y = fmaxf(v.y, 0.f), v.z = fmaxf(v.z, 0.f), v.w = fmaxf(v.w, 0.f);
+            const size_t o = (size_t)row * g.cols + col;
+            if (sizeof(T) == 4) {
+                *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + o) = v;
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                uint2 u;
+                u.x = *reinterpret_cast<uint32_t *>(&lo);
+                u.y = *reinterpret_cast<uint32_t *>(&hi);
+                *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(out) + o) = u;
+            }
         }
     }
 }
@@ -770,6 +803,14 @@ int encode(CUtensorMap *map, bool tf32, bool mn_major, void *base, int rank, con
 {
     EncodeTiledFn fn = get_encode();
     if (!fn) return rz_record_cuda(cudaErrorUnknown, "cuTensorMapEncodeTiled not available");
+    // The encoder is a driver call and wants a context current on this thread.  A thread that has made no
+    // runtime call yet (an autograd worker, say) has none: a null free binds the device's primary context.
+    static thread_local bool bound = false;
+    if (!bound) {
+        int st = rz_record_cuda(cudaFree(nullptr), "bind the primary context");
+        if (st) return st;
+        bound = true;
+    }
     cuuint64_t gdim[3];
     cuuint64_t gstr[2];
     cuuint32_t bx[3], estr[3];
@@ -814,7 +855,8 @@ uint32_t env_u32(const char *name, uint32_t dflt)
 // blocks per pair, block columns.  Blocks are rows = 128*ctas*rb by nc.
 struct TcConfig {
     int ctas, rb, nc;
-    int nsplit;   // parts the contraction is split into (1 = whole contraction per block)
+    int nsplit;   // parts the contraction of the blocks from n_main on is split into (1 = no block is split)
+    int n_main;   // blocks [0, n_main) keep their whole contraction; 0 with nsplit > 1 = every block is split
 };
 
 // Candidates from the largest block down, with the relative tensor throughput each sustains when the grid
@@ -824,7 +866,7 @@ const struct {
     TcConfig cfg;
     double speed;
 } kCandidates[] = {
-    {{2, 2, 256, 1}, 1.00}, {{2, 1, 256, 1}, 0.80}, {{1, 1, 256, 1}, 0.58}, {{1, 1, 128, 1}, 0.40}, {{1, 1, 64, 1}, 0.25},
+    {{2, 2, 256, 1, 0}, 1.00}, {{2, 1, 256, 1, 0}, 0.80}, {{1, 1, 256, 1, 0}, 0.58}, {{1, 1, 128, 1, 0}, 0.40}, {{1, 1, 64, 1, 0}, 0.25},
 };
 
 // Pick the block shape with the best (occupancy of the last wave) x (shape throughput), among the shapes the
@@ -875,18 +917,37 @@ TcConfig choose_config(const rz_problem *pb, int op)
             const int64_t need = (depth + 2047) / 2048;
             if (c.nsplit < need) c.nsplit = (int)need;
         }
+        // Ragged last wave (FWD / DX): the blocks left over after the full waves are split over the idle CTAs, so the
+        // tail costs 1/nsplit of a wave instead of a whole one; only those blocks go through the workspace.
+        const int64_t tail = items % slots;
+        if (!no_split && c.nsplit == 1 && op != RZ_OP_BACKWARD_WEIGHT && items > slots && tail > 0 && tail * 2 <= slots &&
+            stages >= 32) {
+            int64_t s2 = slots / tail, most = stages / 8;
+            if (s2 > most) s2 = most;
+            if (s2 >= 2) {
+                c.nsplit = (int)s2;
+                c.n_main = (int)(items - tail);
+            }
+        }
         if (forced >= 1 && forced <= 5) {
             static const int order[5] = {2, 1, 0, 3, 4};
             if (order[forced - 1] == i) return c;
             continue;
         }
         if (rows < block_rows / 2 && c.ctas * c.rb > 1) continue;   // do not pair CTAs over rows that do not exist
-        const int64_t work = items * c.nsplit;
-        const int64_t waves = (work + slots - 1) / slots;
-        const double occupancy = (double)work / (double)(waves * slots);
+        // time in waves of whole-contraction blocks, against the ideal items / slots
+        double waves;
+        if (c.nsplit == 1) {
+            waves = (double)((items + slots - 1) / slots);
+        } else if (c.n_main == 0) {
+            waves = (double)((items * c.nsplit + slots - 1) / slots) / c.nsplit + 0.1;
+        } else {
+            waves = (double)(c.n_main / slots) + (double)((tail * c.nsplit + slots - 1) / slots) / c.nsplit + 0.1;
+        }
+        const double occupancy = ((double)items / (double)slots) / waves;
         // useful fraction of the block (ragged last row block)
         const double fill = (double)rows / (double)(((rows + block_rows - 1) / block_rows) * block_rows);
-        const double score = occupancy * fill * cand.speed * (c.nsplit > 1 ? 0.9 : 1.0);
+        const double score = (occupancy > 1.0 ? 1.0 : occupancy) * fill * cand.speed;
         if (score > best_score * 1.02) {   // prefer the larger block on near ties
             best_score = score;
             best = c;
@@ -895,14 +956,17 @@ TcConfig choose_config(const rz_problem *pb, int op)
     return best;
 }
 
-// fp32 partial-sum workspace a split FWD / DX launch needs (0 for whole-contraction launches and for DW)
+// fp32 partial-sum workspace a FWD / DX launch with split blocks needs: one block-sized tile per split block
+// (0 for whole-contraction launches and for DW, which adds its parts straight into the hashed gradient)
 size_t workspace_bytes(const rz_problem *pb, int op)
 {
     if (op == RZ_OP_BACKWARD_WEIGHT) return 0;
     const TcConfig c = choose_config(pb, op);
     if (c.nsplit <= 1) return 0;
-    const size_t cols = (op == RZ_OP_BACKWARD_INPUT) ? (size_t)pb->K : (size_t)pb->N;
-    return ((size_t)pb->M * cols * sizeof(float) + 255) / 256 * 256;
+    const int64_t cols = (op == RZ_OP_BACKWARD_INPUT) ? pb->K : pb->N;
+    const int64_t block_rows = (int64_t)TILE_R * c.ctas * c.rb;
+    const int64_t items = ((pb->M + block_rows - 1) / block_rows) * ((cols + c.nc - 1) / c.nc);
+    return (size_t)(items - c.n_main) * (size_t)block_rows * (size_t)c.nc * sizeof(float);
 }
 
 uint32_t dx_box_rows(const rz_problem *pb, const TcConfig &c)
@@ -912,7 +976,7 @@ uint32_t dx_box_rows(const rz_problem *pb, const TcConfig &c)
 }
 
 template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC>
-int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, int nsplit_wanted)
+int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, const TcConfig &plan)
 {
     const rz_problem *pb = c.pb;
     constexpr int ES = TF32 ? 4 : 2;
@@ -966,12 +1030,15 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     }
 
     const uint32_t tiles = p.tiles_r * p.tiles_c;
-    p.nsplit = nsplit_wanted > 1 ? (uint32_t)nsplit_wanted : 1u;
-    if (OP != OP_DW && !p.ws) p.nsplit = 1;   // no workspace given: whole contraction per block
+    p.nsplit = plan.nsplit > 1 ? (uint32_t)plan.nsplit : 1u;
+    p.n_main = plan.nsplit > 1 ? (uint32_t)plan.n_main : tiles;
+    if (OP != OP_DW && !p.ws) p.nsplit = 1, p.n_main = tiles;   // no workspace given: whole contraction per block
+    if (p.n_main > tiles) p.n_main = tiles;
     if (p.nsplit > p.nchunks) p.nsplit = p.nchunks;
     p.chunks_per_split = (p.nchunks + p.nsplit - 1) / p.nsplit;
     p.nsplit = (p.nchunks + p.chunks_per_split - 1) / p.chunks_per_split;
-    p.total_items = tiles * p.nsplit;
+    if (p.nsplit <= 1) p.nsplit = 1, p.n_main = tiles;
+    p.total_items = p.n_main + (tiles - p.n_main) * p.nsplit;
     p.alpha = pb->alpha;
     p.relu = (pb->flags & RZ_FLAG_RELU) ? 1 : 0;
     p.status = rz_device_status_word();
@@ -1004,8 +1071,10 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     const uint32_t blocks = p.total_items < (uint32_t)slots ? p.total_items : (uint32_t)slots;
     cfg.gridDim = dim3(blocks * CTAS, 1, 1);
     const bool partial = OP != OP_DW && p.nsplit > 1;
+    const uint32_t split_tiles = tiles - p.n_main;
     if (partial) {
-        st = rz_record_cuda(cudaMemsetAsync(p.ws, 0, sizeof(float) * (size_t)p.rows * p.cols, c.stream), "zero workspace");
+        st = rz_record_cuda(cudaMemsetAsync(p.ws, 0, sizeof(float) * (size_t)split_tiles * ITEM_R * NC, c.stream),
+                            "zero workspace");
         if (st) return st;
     }
     st = rz_record_cuda(cudaLaunchKernelEx(&cfg, kern, mapA, mapB, p), "tcgen05 kernel launch");
@@ -1013,16 +1082,19 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     if (st) return st;
     st = rz_record_cuda(cudaGetLastError(), "tcgen05 kernel launch");
     if (st || !partial) return st;
-    const size_t n4 = (size_t)p.rows * p.cols / 4;
-    unsigned fblocks = (unsigned)((n4 + 255) / 256);
-    if (fblocks > 148u * 8u) fblocks = 148u * 8u;
+    FinalizeGeom fg;
+    fg.rows = p.rows, fg.cols = p.cols, fg.item_r = ITEM_R, fg.nc = NC, fg.tiles_r = p.tiles_r, fg.tiles_c = p.tiles_c;
+    fg.group_rows = p.group_rows, fg.n_main = p.n_main, fg.n_tiles = tiles;
+    // about four CTAs per SM in total, several per block when few blocks were split
+    unsigned per_tile = (148u * 4u + split_tiles - 1) / split_tiles;
+    if (per_tile > 32u) per_tile = 32u;
+    const dim3 fblocks(split_tiles < 148u * 4u ? split_tiles : 148u * 4u, per_tile, 1);
     const float *fbias = OP == OP_FWD ? p.bias : nullptr;   // bias and ReLU belong to the forward pass only
     const int frelu = OP == OP_FWD ? p.relu : 0;
     if (TF32)
-        rz_finalize_kernel<float><<<fblocks, 256, 0, c.stream>>>(p.ws, (float *)p.out, fbias, p.rows, p.cols, p.alpha, frelu);
+        rz_finalize_kernel<float><<<fblocks, 256, 0, c.stream>>>(p.ws, (float *)p.out, fbias, fg, p.alpha, frelu);
     else
-        rz_finalize_kernel<__nv_bfloat16><<<fblocks, 256, 0, c.stream>>>(p.ws, (__nv_bfloat16 *)p.out, fbias, p.rows, p.cols,
-                                                                          p.alpha, frelu);
+        rz_finalize_kernel<__nv_bfloat16><<<fblocks, 256, 0, c.stream>>>(p.ws, (__nv_bfloat16 *)p.out, fbias, fg, p.alpha, frelu);
     rz_count_launch(1);
     return rz_record_cuda(cudaGetLastError(), "finalize launch");
 }
@@ -1032,21 +1104,21 @@ int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorM
 {
     const int prec = c.pb->precision;
     if (prec == RZ_PREC_FP32) {   // split precision: fp32 operands, three tf32 MMAs per product
-        if (cfg.ctas == 2) return launch_tc<OP, true, 2, 1, 1, 256>(c, mapA, mapB, p, cfg.nsplit);
-        if (cfg.nc == 256) return launch_tc<OP, true, 1, 1, 1, 256>(c, mapA, mapB, p, cfg.nsplit);
-        if (cfg.nc == 128) return launch_tc<OP, true, 1, 1, 1, 128>(c, mapA, mapB, p, cfg.nsplit);
-        return launch_tc<OP, true, 1, 1, 1, 64>(c, mapA, mapB, p, cfg.nsplit);
+        if (cfg.ctas == 2) return launch_tc<OP, true, 2, 1, 1, 256>(c, mapA, mapB, p, cfg);
+        if (cfg.nc == 256) return launch_tc<OP, true, 1, 1, 1, 256>(c, mapA, mapB, p, cfg);
+        if (cfg.nc == 128) return launch_tc<OP, true, 1, 1, 1, 128>(c, mapA, mapB, p, cfg);
+        return launch_tc<OP, true, 1, 1, 1, 64>(c, mapA, mapB, p, cfg);
     }
     const bool tf32 = prec == RZ_PREC_TF32;
     if (cfg.ctas == 2 && cfg.rb == 2)
-        return tf32 ? launch_tc<OP, true, 2, 2, 0, 256>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 2, 2, 0, 256>(c, mapA, mapB, p, cfg.nsplit);
+        return tf32 ? launch_tc<OP, true, 2, 2, 0, 256>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 2, 2, 0, 256>(c, mapA, mapB, p, cfg);
     if (cfg.ctas == 2)
-        return tf32 ? launch_tc<OP, true, 2, 1, 0, 256>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 2, 1, 0, 256>(c, mapA, mapB, p, cfg.nsplit);
+        return tf32 ? launch_tc<OP, true, 2, 1, 0, 256>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 2, 1, 0, 256>(c, mapA, mapB, p, cfg);
     if (cfg.nc == 256)
-        return tf32 ? launch_tc<OP, true, 1, 1, 0, 256>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 1, 1, 0, 256>(c, mapA, mapB, p, cfg.nsplit);
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 256>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 256>(c, mapA, mapB, p, cfg);
     if (cfg.nc == 128)
-        return tf32 ? launch_tc<OP, true, 1, 1, 0, 128>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 1, 1, 0, 128>(c, mapA, mapB, p, cfg.nsplit);
-    return tf32 ? launch_tc<OP, true, 1, 1, 0, 64>(c, mapA, mapB, p, cfg.nsplit) : launch_tc<OP, false, 1, 1, 0, 64>(c, mapA, mapB, p, cfg.nsplit);
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 128>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 128>(c, mapA, mapB, p, cfg);
+    return tf32 ? launch_tc<OP, true, 1, 1, 0, 64>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 64>(c, mapA, mapB, p, cfg);
 }
 
 // 2-D map over a row-major matrix [rows][cols] of the operand type
