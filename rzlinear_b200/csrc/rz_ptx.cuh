@@ -29,6 +29,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive without release semantics: for hand-offs whose payload is not memory (a TMEM accumulator that has been
+// read into registers), so the arrive need not wait for the thread's global reductions still in flight.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -223,6 +229,10 @@ __device__ __forceinline__ uint32_t mapa_cluster(uint32_t local_addr, uint32_t c
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA loads issued by either CTA of a pair: data lands in the issuing CTA's shared memory, the
 // transaction bytes are reported to `bar_cluster`, a shared::cluster mbarrier address (the leader's).

@@ -63,20 +63,21 @@ constexpr int MAX_STAGES = 7;
 constexpr int SMEM_BARS = (3 * MAX_STAGES + 5) * 8;
 constexpr int SMEM_LIMIT = 232448;
 // per epilogue warp: a 32x33 fp32 transpose tile (DW) or a 32-row x 128-byte store staging tile (FWD, DX)
-__host__ __device__ constexpr int smem_epi(int op, int rb) { return 4 * rb * (op == OP_DW ? SMEM_EPI_WARP : 4096); }
+// `ew`: epilogue warps per TMEM lane quarter and row block (weight gradient of short contractions: 4)
+__host__ __device__ constexpr int smem_epi(int op, int rb, int ew = 1) { return 4 * rb * ew * (op == OP_DW ? SMEM_EPI_WARP : 4096); }
 __host__ __device__ constexpr int load_bytes(int ctas, int rb, int nc) { return rb * A_BLOCK_BYTES + (nc / ctas) * 128; }
 __host__ __device__ constexpr int stage_bytes(int ctas, int rb, int split, int nc) { return load_bytes(ctas, rb, nc) * (split ? 2 : 1); }
-__host__ __device__ constexpr int num_stages(int op, int ctas, int rb, int split, int nc)
+__host__ __device__ constexpr int num_stages(int op, int ctas, int rb, int split, int nc, int ew = 1)
 {
-    int n = (SMEM_LIMIT - 1024 - 16 - SMEM_BARS - SMEM_TABLE - smem_epi(op, rb)) / stage_bytes(ctas, rb, split, nc);
+    int n = (SMEM_LIMIT - 1024 - 16 - SMEM_BARS - SMEM_TABLE - smem_epi(op, rb, ew)) / stage_bytes(ctas, rb, split, nc);
     return n > MAX_STAGES ? MAX_STAGES : n;
 }
-__host__ __device__ constexpr int smem_total(int op, int ctas, int rb, int split, int nc)
+__host__ __device__ constexpr int smem_total(int op, int ctas, int rb, int split, int nc, int ew = 1)
 {
-    return num_stages(op, ctas, rb, split, nc) * stage_bytes(ctas, rb, split, nc) + smem_epi(op, rb) + SMEM_TABLE + SMEM_BARS +
+    return num_stages(op, ctas, rb, split, nc, ew) * stage_bytes(ctas, rb, split, nc) + smem_epi(op, rb, ew) + SMEM_TABLE + SMEM_BARS +
            16 + 1024;
 }
-__host__ __device__ constexpr int num_threads(int rb, int split) { return 64 + 128 * rb + (split ? 128 : 0); }
+__host__ __device__ constexpr int num_threads(int rb, int split, int ew = 1) { return 64 + 128 * rb * ew + (split ? 128 : 0); }
 
 struct TcParams {
     RzHash hash;
@@ -109,8 +110,8 @@ __device__ __forceinline__ void wait_cycles(uint32_t bar, uint32_t parity, long 
         if (clock64() - t0 > cycles) break;
 }
 
-template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC>
-__global__ void __launch_bounds__(num_threads(RB, SPLIT), 1)
+template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC, int EW>
+__global__ void __launch_bounds__(num_threads(RB, SPLIT, EW), 1)
 rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
 {
     constexpr int ES = TF32 ? 4 : 2;        // operand element size
@@ -125,12 +126,13 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     constexpr int A_BYTES = RB * A_BLOCK_BYTES;
     constexpr int LOAD_BYTES = A_BYTES + B_BYTES;                 // what TMA brings per stage and CTA
     constexpr int STAGE_BYTES = LOAD_BYTES * (SPLIT ? 2 : 1);     // SPLIT: the lo parts sit LOAD_BYTES above the hi parts
-    constexpr int STAGES = num_stages(OP, CTAS, RB, SPLIT, NC);
+    constexpr int STAGES = num_stages(OP, CTAS, RB, SPLIT, NC, EW);
     constexpr bool PAIR_LOADS = (CTAS == 2) && !SPLIT;            // loads of both CTAs counted on the leader's barrier
-    constexpr int EPI_WARPS = 4 * RB;
+    constexpr int EPI_WARPS = 4 * RB * EW;
+    static_assert(EW == 1 || (OP == OP_DW && RB == 1 && !SPLIT), "extra epilogue warps: weight gradient, one row block");
     static_assert(!SPLIT || (TF32 && RB == 1), "split precision: fp32 operands, one row block");
     constexpr int SMEM_RING = STAGES * STAGE_BYTES;
-    constexpr int SMEM_EPI_OP = smem_epi(OP, RB);
+    constexpr int SMEM_EPI_OP = smem_epi(OP, RB, EW);
     // accumulator sets in TMEM: 2 = double-buffered; 1 when both halves are in use by one block (two row blocks, or
     // the main + correction accumulators of split precision)
     constexpr int NBUF = (RB == 2 || SPLIT) ? 1 : 2;
@@ -178,7 +180,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_tfull + 8 * b, 1);
-            mbar_init(bar_tempty + 8 * b, 4 * RB * CTAS);
+            mbar_init(bar_tempty + 8 * b, EPI_WARPS * CTAS);
         }
         mbar_init(bar_drain, 1);
         fence_barrier_init();
@@ -394,7 +396,12 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     } else if (warp < 2 + EPI_WARPS) {
         // ===================== epilogue (both CTAs; each drains its own 128 rows) =====================
         const uint32_t q = warp & 3;          // TMEM lane quarter this warp may read
-        const uint32_t rblk = (warp - 2) >> 2;  // which accumulator (row block) of the item this warp drains
+        const uint32_t rblk = EW > 1 ? 0u : (warp - 2) >> 2;  // which accumulator (row block) of the item this warp drains
+        const uint32_t cgrp = EW > 1 ? (warp - 2) >> 2 : 0u;  // EW > 1: this warp takes the 32-column chunks cgrp, cgrp + EW, ...
+        uint32_t own = 0;                                     // mask of those chunks
+#pragma unroll
+        for (int c2 = 0; c2 < TILE_C / 32; ++c2)
+            if (c2 % EW == (int)cgrp) own |= 1u << c2;
         float *scratch = epi_scratch + (warp - 2) * (OP == OP_DW ? 32 * 33 : 1024);
         uint32_t tempty_base = bar_tempty;
         if (CTAS == 2) tempty_base = mapa_cluster(bar_tempty, 0);
@@ -428,12 +435,78 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     if (o2 == key_off && r2 == key_rel) eqmask |= 1u << c2;
                 }
             }
+            if (OP == OP_DW && EW > 1) {
+                // Scatter-bound weight gradient.  The warp pulls all its chunks out of TMEM at once and hands the
+                // accumulator back before it starts on the reductions, so the next blocks' MMAs never wait for the
+                // scatter; loads from TMEM then come in one short burst per block instead of trickling in between
+                // the MMAs for the whole epilogue.
+                constexpr int NCH = (TILE_C / 32 + EW - 1) / EW;   // chunks per warp
+                uint32_t vv[NCH][32];
+#pragma unroll
+                for (int j = 0; j < NCH; ++j) {
+                    const int c = (int)cgrp + j * EW;
+                    if (c < TILE_C / 32) tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + buf * TILE_C + c * 32, vv[j]);
+                }
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {   // relaxed: a release would wait for the previous block's reductions still in flight
+                    if (CTAS == 2) mbar_arrive_cluster_relaxed(tempty_base + 8 * buf);
+                    else mbar_arrive_relaxed(bar_tempty + 8 * buf);
+                }
+                const uint32_t kb = rbase;
+                if (kb >= p.K) continue;
+                const uint32_t nrow = min(32u, p.K - kb);
+                const uint32_t row_in = kb - (kb / (uint32_t)p.hash.BK) * (uint32_t)p.hash.BK;
+                const uint32_t bn = (uint32_t)p.hash.BN;
+#pragma unroll
+                for (int j = 0; j < NCH; ++j) {
+                    const int c = (int)cgrp + j * EW;
+                    if (c >= TILE_C / 32) break;
+                    const uint32_t same = __shfl_sync(0xffffffffu, eqmask, c) & own;
+                    if (same & ((1u << c) - 1u)) continue;   // summed into an earlier chunk of this warp
+                    bool col_ok = tc * TILE_C + c * 32 + lane < p.N;
+                    float acc[32];
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(vv[j][e]);
+#pragma unroll
+                    for (int j2 = j + 1; j2 < NCH; ++j2) {
+                        const int c2 = (int)cgrp + j2 * EW;
+                        if (c2 < TILE_C / 32 && ((same >> c2) & 1u)) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) acc[e] += __uint_as_float(vv[j2][e]);
+                            col_ok = col_ok || (tc * TILE_C + c2 * 32 + lane < p.N);
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) scratch[lane * 33 + e] = acc[e] * p.alpha;
+                    __syncwarp();
+                    const uint32_t off = __shfl_sync(0xffffffffu, key_off, c), rel = __shfl_sync(0xffffffffu, key_rel, c);
+                    float *dst = p.dH + off + (uint64_t)row_in * bn + rel + lane;
+                    if (nrow == 32) {
+#pragma unroll
+                        for (int r0 = 0; r0 < 32; r0 += 8) {
+                            float t[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) t[e] = scratch[(r0 + e) * 33 + lane];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (col_ok) atomicAdd(dst + (size_t)(r0 + e) * bn, t[e]);
+                        }
+                    } else {
+                        for (uint32_t rr = 0; rr < nrow; ++rr)
+                            if (col_ok) atomicAdd(dst + (size_t)rr * bn, scratch[rr * 33 + lane]);
+                    }
+                    __syncwarp();
+                }
+                continue;
+            }
 #pragma unroll 1
-            for (int c = 0; c < TILE_C / 32; ++c) {
+            for (int c = (int)cgrp; c < TILE_C / 32; c += EW) {
                 uint32_t v[32];
                 uint32_t same = 0;
                 if (OP == OP_DW) {
-                    same = __shfl_sync(0xffffffffu, eqmask, c);
+                    same = __shfl_sync(0xffffffffu, eqmask, c) & own;   // merge only among this warp's chunks
                     if (same & ((1u << c) - 1u)) continue;   // already merged into an earlier chunk
                 }
                 tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + (buf * RB + rblk) * TILE_C + c * 32, v);
@@ -857,6 +930,7 @@ struct TcConfig {
     int ctas, rb, nc;
     int nsplit;   // parts the contraction of the blocks from n_main on is split into (1 = no block is split)
     int n_main;   // blocks [0, n_main) keep their whole contraction; 0 with nsplit > 1 = every block is split
+    int ew;       // epilogue warps per TMEM lane quarter (0 or 1 = one; 4 = weight gradient of a short contraction)
 };
 
 // Candidates from the largest block down, with the relative tensor throughput each sustains when the grid
@@ -929,6 +1003,10 @@ TcConfig choose_config(const rz_problem *pb, int op)
                 c.n_main = (int)(items - tail);
             }
         }
+        // Weight gradient of a short contraction: the scatter epilogue (one reduction per 32 elements, issued by
+        // one warp per scheduler) outlasts the main loop; sixteen epilogue warps hide its instruction latency.
+        if (op == RZ_OP_BACKWARD_WEIGHT && !split && c.rb == 1 && stages / c.nsplit <= (int64_t)env_u32("RZ_TC_EW_STAGES", 64))
+            c.ew = 4;
         if (forced >= 1 && forced <= 5) {
             static const int order[5] = {2, 1, 0, 3, 4};
             if (order[forced - 1] == i) return c;
@@ -975,7 +1053,7 @@ uint32_t dx_box_rows(const rz_problem *pb, const TcConfig &c)
     return (uint32_t)pb->BK < bcols ? (uint32_t)pb->BK : bcols;
 }
 
-template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC>
+template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC, int EW = 1>
 int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, const TcConfig &plan)
 {
     const rz_problem *pb = c.pb;
@@ -984,7 +1062,7 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     constexpr int KC = EPR;
     constexpr int PAIR_R = TILE_R * CTAS;
     constexpr int ITEM_R = PAIR_R * RB;
-    constexpr int NTHREADS = num_threads(RB, SPLIT);
+    constexpr int NTHREADS = num_threads(RB, SPLIT, EW);
     p.hash = c.hash;
     p.M = (uint32_t)pb->M;
     p.K = (uint32_t)pb->K;
@@ -999,8 +1077,8 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.group_rows = env_u32("RZ_TC_GROUP", GROUP_ROWS / RB);
     if (p.group_rows < 1) p.group_rows = 1;
 
-    auto kern = rz_tc_kernel<OP, TF32, CTAS, RB, SPLIT, NC>;
-    constexpr int SMEM_TOTAL = smem_total(OP, CTAS, RB, SPLIT, NC);
+    auto kern = rz_tc_kernel<OP, TF32, CTAS, RB, SPLIT, NC, EW>;
+    constexpr int SMEM_TOTAL = smem_total(OP, CTAS, RB, SPLIT, NC, EW);
     static_assert(SMEM_TOTAL <= SMEM_LIMIT, "shared memory budget");
     int st = rz_record_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL),
                             "set max dynamic shared memory");
@@ -1110,6 +1188,16 @@ int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorM
         return launch_tc<OP, true, 1, 1, 1, 64>(c, mapA, mapB, p, cfg);
     }
     const bool tf32 = prec == RZ_PREC_TF32;
+    if (OP == OP_DW && cfg.ew == 4 && cfg.rb == 1) {   // scatter-bound weight gradient: sixteen epilogue warps
+        constexpr int W = (OP == OP_DW) ? 4 : 1;       // (keeps the other operations from instantiating the variant)
+        if (cfg.ctas == 2)
+            return tf32 ? launch_tc<OP, true, 2, 1, 0, 256, W>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 2, 1, 0, 256, W>(c, mapA, mapB, p, cfg);
+        if (cfg.nc == 256)
+            return tf32 ? launch_tc<OP, true, 1, 1, 0, 256, W>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 256, W>(c, mapA, mapB, p, cfg);
+        if (cfg.nc == 128)
+            return tf32 ? launch_tc<OP, true, 1, 1, 0, 128, W>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 128, W>(c, mapA, mapB, p, cfg);
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 64, W>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 64, W>(c, mapA, mapB, p, cfg);
+    }
     if (cfg.ctas == 2 && cfg.rb == 2)
         return tf32 ? launch_tc<OP, true, 2, 2, 0, 256>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 2, 2, 0, 256>(c, mapA, mapB, p, cfg);
     if (cfg.ctas == 2)
