@@ -136,6 +136,14 @@ int rz_linear_backward_weight(const rz_problem *pb, const void *X, const void *d
    Replaces rz_linear_idx_tl, python/rz_linear/impl/RzLinearIdx.py:6-45. */
 int rz_linear_materialize(const rz_problem *pb, const float *hashed, float *W, void *stream);
 
+/* Backward-pass preparation for a layer whose bias add and ReLU were fused into rz_linear_forward, in one pass
+   over the incoming gradient dY[M,N]: with Y != NULL (the layer's saved output) dYm = dY where Y > 0, else 0;
+   with bias_grad != NULL, bias_grad[n] = sum over m of the (masked) gradient, fp32 [N], zeroed first.  dYm may be
+   NULL when Y is NULL (bias gradient only).  Replaces the separate torch ops of the reference's module
+   (python/rz_linear/RzLinear.py:93-94 adds the bias outside the kernel, so autograd sums it there). */
+int rz_grad_prepare(const rz_problem *pb, const void *dY, const void *Y, void *dYm, float *bias_grad,
+                    void *stream);
+
 /* hashed -= lr * dH, and (when shadow != NULL) the shadow copies are rewritten in the same pass.
    No counterpart in the reference (its optimiser step is torch's); used by the data-parallel step. */
 int rz_sgd_step(const rz_problem *pb, float *hashed, const float *dH, float lr, void *shadow,

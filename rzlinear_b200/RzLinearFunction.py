@@ -88,13 +88,21 @@ class RzLinearFunction(torch.autograd.Function):
         R = _unpack(random_numbers)
         M, K, N, H = input.shape[0], input.shape[1], ctx.output_dim, hashed_weight.shape[0]
         grad = grad.contiguous()
-        if cfg.relu:
-            grad = grad * (out > 0).to(grad.dtype)
         x = input.contiguous()
         hashed = launchers._hashed_f32(hashed_weight)
         pb = launchers.make_problem(M, K, N, H, R, cfg.block_size_k, cfg.block_size_n, x.dtype, ctx.allow_tf32,
                                     ctx.init_factor, cfg.hash_mode)
         input_grad = weight_grad = bias_grad = None
+        # one pass over the incoming gradient: ReLU mask from the saved output and the bias gradient (column sums)
+        want_bias = ctx.has_bias and ctx.needs_input_grad[7]
+        if cfg.relu or want_bias:
+            if grad.dtype != x.dtype:
+                grad = grad.to(x.dtype)
+            masked = torch.empty_like(grad) if cfg.relu else None
+            bias_grad = torch.empty((N,), device=x.device, dtype=torch.float32) if want_bias else None
+            _lib.grad_prepare(pb, grad, out if cfg.relu else None, masked, bias_grad)
+            if cfg.relu:
+                grad = masked
         if ctx.needs_input_grad[0]:
             input_grad = torch.empty((M, K), device=x.device, dtype=x.dtype)
             _lib.backward_input(pb, grad, hashed, ctx.shadow, input_grad)
@@ -102,7 +110,5 @@ class RzLinearFunction(torch.autograd.Function):
             dh = torch.empty((H,), device=x.device, dtype=torch.float32)
             _lib.backward_weight(pb, x, grad, dh)
             weight_grad = dh if hashed_weight.dtype == torch.float32 else dh.to(hashed_weight.dtype)
-        if ctx.has_bias and ctx.needs_input_grad[7]:
-            bias_grad = grad.float().sum(dim=0)
         ctx.shadow = None
         return input_grad, weight_grad, None, None, None, None, None, bias_grad

@@ -28,7 +28,7 @@ EXPORTS = [
     "rz_hash_indices_device", "rz_plan", "rz_shadow_bytes", "rz_shadow_refresh",
     "rz_linear_forward", "rz_linear_backward_input", "rz_linear_backward_weight",
     "rz_linear_materialize", "rz_sgd_step", "rz_device_status", "rz_launch_count",
-    "rz_selftest_bounded_wait", "rz_sgd_momentum_step",
+    "rz_selftest_bounded_wait", "rz_sgd_momentum_step", "rz_grad_prepare",
 ]
 
 
@@ -82,6 +82,8 @@ def load() -> ctypes.CDLL:
         lib.rz_linear_backward_input.argtypes = [pbp, vp, vp, vp, vp, vp]
         lib.rz_linear_backward_weight.argtypes = [pbp, vp, vp, vp, vp]
         lib.rz_linear_materialize.argtypes = [pbp, vp, vp, vp]
+        lib.rz_grad_prepare.argtypes = [pbp, vp, vp, vp, vp, vp]
+        lib.rz_grad_prepare.restype = ctypes.c_int
         lib.rz_sgd_step.argtypes = [pbp, vp, vp, ctypes.c_float, vp, vp]
         lib.rz_device_status.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         lib.rz_launch_count.restype = ctypes.c_uint64
@@ -198,6 +200,13 @@ def materialize(pb, hashed, w) -> None:
     _require_cuda(hashed, w)
     with torch.cuda.device(hashed.device):
         check(load().rz_linear_materialize(ctypes.byref(pb), _ptr(hashed), _ptr(w), _stream(hashed.device)))
+
+
+def grad_prepare(pb, dy, y, dym, bias_grad) -> None:
+    """dym = dy where y > 0 (y may be None: no mask), bias_grad = column sums of the (masked) gradient (may be None)."""
+    _require_cuda(dy, y, dym, bias_grad)
+    with torch.cuda.device(dy.device):
+        check(load().rz_grad_prepare(ctypes.byref(pb), _ptr(dy), _ptr(y), _ptr(dym), _ptr(bias_grad), _stream(dy.device)))
 
 
 def sgd_step(pb, hashed, dh, lr, shadow) -> None:

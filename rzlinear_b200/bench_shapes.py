@@ -5,6 +5,8 @@ hashed-weight gradient and input gradient, TFLOPS = 2*M*N*K / time, `torch.matmu
 the same shape as the comparison line; once with tf32 tensor cores allowed and once in fp32.
 
     python -m rzlinear_b200.bench_shapes [--dtype fp32|tf32|bf16] [--reps 20]
+    python -m rzlinear_b200.bench_shapes --baseline          # the single-layer and MLP baseline configurations
+    python -m rzlinear_b200.bench_shapes --dtype bf16 --shape 128,10240,10240 [--hashed H --block BK,BN]
 
 Prints one JSON line per shape and precision.
 """
@@ -36,16 +38,22 @@ def _time(fn, reps):
     return e0.elapsed_time(e1) / reps
 
 
-def run(precision: str, reps: int, block_k: int = 32, block_n: int = 64, device="cuda:0"):
+# Single-layer baseline configurations: (precision, M, K, N, H, BK, BN)
+BASELINE = [("fp32", 1024, 1024, 1024, 65536, 32, 32),
+            ("tf32", 16384, 4096, 4096, 1 << 20, 64, 64),
+            ("bf16", 8192, 8192, 32768, 1 << 22, 128, 128)]
+
+
+def run(precision: str, reps: int, block_k: int = 32, block_n: int = 64, device="cuda:0", shapes=None, hashed=None):
     dev = torch.device(device)
     dtype = torch.bfloat16 if precision == "bf16" else torch.float32
     prec = {"fp32": _lib.PREC_FP32, "tf32": _lib.PREC_TF32, "bf16": _lib.PREC_BF16}[precision]
-    if precision == "bf16":
+    if precision == "bf16" and shapes is None:
         block_k = max(block_k, 64)
     torch.backends.cuda.matmul.allow_tf32 = precision == "tf32"
     R = [PRIME] + [int(v) for v in np.random.RandomState(0).randint(1, 2**31 - 1, 7)]
-    for (M, K, N) in CONFIGS:
-        H = int(K * N * 0.0625)                     # the reference's default compress_ratio
+    for (M, K, N) in (shapes or CONFIGS):
+        H = hashed or int(K * N * 0.0625)           # default: the reference's default compress_ratio
         pb = _lib.make_problem(M, K, N, H, block_k, block_n, R, _lib.HASH_SINGLE, _lib.torch_io_dtype(dtype), prec)
         g = torch.Generator(device=dev).manual_seed(0)
         X = torch.randn((M, K), generator=g, device=dev).to(dtype)
@@ -74,10 +82,59 @@ def run(precision: str, reps: int, block_k: int = 32, block_n: int = 64, device=
                           "tflops": {k: round(v, 2) for k, v in tflops.items()}}), flush=True)
 
 
+def run_mlp(reps: int, batch: int = 65536, dims=(1024, 4096, 4096, 256), hashed: int = 1 << 18, device="cuda:0"):
+    """Full training step (forward, MSE loss, backward) of the 3-layer ReLU MLP baseline configuration in bf16,
+    next to the same MLP built from dense torch.nn.Linear layers (cuBLAS).  The input needs no gradient, so the
+    step runs 3 forward, 3 weight-gradient and 2 input-gradient products."""
+    from .RzLinear import RzLinear
+    dev = torch.device(device)
+    torch.manual_seed(4)
+    rs = np.random.RandomState(4)
+    ours = torch.nn.ModuleList([
+        RzLinear(dims[i], dims[i + 1], hashed_weight=torch.nn.Parameter((torch.rand(hashed) * 2 - 1) / dims[i] ** 0.5),
+                 hash_mode="single", random_numbers=[PRIME] + [int(v) for v in rs.randint(1, 2**31 - 1, 3)] + [0, 0, 0, 0],
+                 block_size_k=64, block_size_n=64, relu=(i < 2)) for i in range(3)]).to(dev)
+    dense = torch.nn.ModuleList([torch.nn.Linear(dims[i], dims[i + 1]) for i in range(3)]).to(dev).to(torch.bfloat16)
+    x = torch.randn(batch, dims[0], device=dev).to(torch.bfloat16)
+    target = torch.randn(batch, dims[-1], device=dev).to(torch.bfloat16)
+
+    def step_ours():
+        y = x
+        for layer in ours:
+            y = layer(y)
+        torch.nn.functional.mse_loss(y.float(), target.float()).backward()
+
+    def step_dense():
+        y = x
+        for i, layer in enumerate(dense):
+            y = layer(y)
+            if i < 2:
+                y = torch.relu(y)
+        torch.nn.functional.mse_loss(y.float(), target.float()).backward()
+
+    flops = 2.0 * batch * (3 * sum(dims[i] * dims[i + 1] for i in range(3)) - dims[0] * dims[1])
+    ms = {"rz_mlp_step": _time(step_ours, reps), "dense_mlp_step": _time(step_dense, reps)}
+    print(json.dumps({"config": "mlp", "batch": batch, "dims": list(dims), "H": hashed, "ms": {k: round(v, 3) for k, v in ms.items()},
+                      "tflops": {k: round(flops * 1e-12 / (v * 1e-3), 1) for k, v in ms.items()}}), flush=True)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--dtype", default="all", choices=["all", "fp32", "tf32", "bf16"])
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--baseline", action="store_true", help="run the baseline configurations instead of the sweep")
+    ap.add_argument("--shape", default=None, help="M,K,N: one shape instead of the sweep")
+    ap.add_argument("--hashed", type=int, default=None, help="length of the hashed array (default K*N/16)")
+    ap.add_argument("--block", default=None, help="BK,BN hash tile (default 32,64; 64,64 for bf16)")
     a = ap.parse_args()
-    for p in (["tf32", "fp32", "bf16"] if a.dtype == "all" else [a.dtype]):
-        run(p, a.reps)
+    if a.baseline:
+        for (prec, M, K, N, H, bk, bn) in BASELINE:
+            run(prec, a.reps, bk, bn, shapes=[(M, K, N)], hashed=H)
+        run_mlp(a.reps)
+    else:
+        shapes = [tuple(int(v) for v in a.shape.split(","))] if a.shape else None
+        bk, bn = (int(v) for v in a.block.split(",")) if a.block else (32, 64)
+        for p in (["tf32", "fp32", "bf16"] if a.dtype == "all" else [a.dtype]):
+            if shapes and not a.block and p == "bf16":
+                bk = 64
+            run(p, a.reps, bk, bn, shapes=shapes, hashed=a.hashed)

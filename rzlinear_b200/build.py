@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "librzlinear_b200.so")
-SOURCES = ["rz_abi.cu", "rz_simt.cu", "rz_tc.cu", "rz_noalloc.cu"]
+SOURCES = ["rz_abi.cu", "rz_simt.cu", "rz_tc.cu", "rz_noalloc.cu", "rz_elementwise.cu"]
 HEADERS = ["rz_common.h", "rz_hash.h", "rz_ptx.cuh", os.path.join("..", "..", "include", "rzlinear_b200.h")]
 
 

@@ -214,6 +214,14 @@ int rz_linear_materialize(const rz_problem *pb, const float *hashed, float *W, v
     return rz_simt_materialize(make_ctx(pb, stream), hashed, W);
 }
 
+int rz_grad_prepare(const rz_problem *pb, const void *dY, const void *Y, void *dYm, float *bias_grad, void *stream)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!dY || (Y && !dYm) || (!dYm && !bias_grad)) return RZ_ERR_NULL;
+    return rz_elementwise_grad_prepare(make_ctx(pb, stream), dY, Y, dYm, bias_grad);
+}
+
 int rz_sgd_step(const rz_problem *pb, float *hashed, const float *dH, float lr, void *shadow, void *stream)
 {
     int st = validate(pb);

@@ -34,6 +34,7 @@ int rz_simt_forward(const RzLaunchCtx &c, const void *X, const float *hashed, co
 int rz_simt_backward_input(const RzLaunchCtx &c, const void *dY, const float *hashed, void *dX);
 int rz_simt_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, float *dH);
 int rz_simt_materialize(const RzLaunchCtx &c, const float *hashed, float *W);
+int rz_elementwise_grad_prepare(const RzLaunchCtx &c, const void *dY, const void *Y, void *dYm, float *bias_grad);
 int rz_simt_hash_indices(const RzLaunchCtx &c, int64_t *out);
 
 // tcgen05 family (rz_tc.cu)

@@ -501,6 +501,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 }
                 continue;
             }
+#pragma nv_diag_suppress 128   // (the EW > 1 instantiations never reach the generic chunk loop)
 #pragma unroll 1
             for (int c = (int)cgrp; c < TILE_C / 32; c += EW) {
                 uint32_t v[32];

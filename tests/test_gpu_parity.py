@@ -173,6 +173,39 @@ def test_accumulate_flag_and_relu_bias(rzlib, L):
     assert o.rel_l2(dh.cpu().numpy(), 2 * o.backward_weight(X.numpy(), dY.numpy(), H, BK, BN, R, 0)) < TOL_FP32
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N", [(257, 512), (64, 100), (1, 8), (3000, 4096)])
+def test_grad_prepare_masks_and_sums(rzlib, dtype, M, N):
+    # backward of the fused bias + ReLU epilogue: masked gradient bit-identical to the elementwise definition,
+    # bias gradient = fp64 column sums within fp32 accumulation error
+    g = torch.Generator().manual_seed(M * 7 + N)
+    dY = torch.randn(M, N, generator=g).to(dtype)
+    Y = torch.relu(torch.randn(M, N, generator=g)).to(dtype)
+    pb = rzlib.make_problem(M, 64, N, 70000, 32, 32, seeded_R(1), 0, rzlib.torch_io_dtype(dtype),
+                            rzlib.PREC_BF16 if dtype == torch.bfloat16 else rzlib.PREC_FP32)
+    dYd, Yd = dY.to(DEV), Y.to(DEV)
+    masked = torch.full((M, N), 7.0, device=DEV, dtype=dtype)
+    bg = torch.full((N,), 7.0, device=DEV)
+    rzlib.grad_prepare(pb, dYd, Yd, masked, bg)
+    want = torch.where(Y > 0, dY, torch.zeros_like(dY))
+    assert torch.equal(masked.cpu(), want)
+    ref = want.double().sum(0).numpy()
+    assert np.abs(bg.cpu().numpy() - ref).max() <= 1e-5 * max(1.0, np.abs(want.double()).sum(0).max())
+    # bias gradient alone (no mask, nothing written)
+    bg2 = torch.empty((N,), device=DEV)
+    rzlib.grad_prepare(pb, dYd, None, None, bg2)
+    ref2 = dY.double().sum(0).numpy()
+    assert np.abs(bg2.cpu().numpy() - ref2).max() <= 1e-5 * max(1.0, dY.double().abs().sum(0).max().item())
+    # mask alone; a misaligned view takes the scalar path
+    if N > 8:
+        flat = torch.empty(M * N + 1, device=DEV, dtype=dtype)
+        dv = flat[1:].view(M, N)
+        dv.copy_(dYd)
+        m2 = torch.empty((M, N), device=DEV, dtype=dtype)
+        rzlib.grad_prepare(pb, dv, Yd, m2, None)
+        assert torch.equal(m2.cpu(), want)
+
+
 # ---------------------------------------------------------------------------------------------
 # module / autograd
 # ---------------------------------------------------------------------------------------------

@@ -104,6 +104,7 @@ def test_null_pointers_are_rejected_before_any_launch(rzlib):
     assert lib.rz_linear_backward_input(ctypes.byref(pb), None, None, None, None, None) == -1
     assert lib.rz_linear_backward_weight(ctypes.byref(pb), None, None, None, None) == -1
     assert lib.rz_linear_materialize(ctypes.byref(pb), None, None, None) == -1
+    assert lib.rz_grad_prepare(ctypes.byref(pb), None, None, None, None, None) == -1
     assert lib.rz_hash_indices_host(None, None) == -1
     assert lib.rz_status_string(-3).decode().startswith("hashed array too small")
 
