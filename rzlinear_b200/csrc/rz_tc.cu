@@ -447,7 +447,8 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     const int c = (int)cgrp + j * EW;
                     if (c < TILE_C / 32) tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + buf * TILE_C + c * 32, vv[j]);
                 }
-                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < NCH; ++j) tmem_ld_wait_regs(vv[j]);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {   // relaxed: a release would wait for the previous block's reductions still in flight
@@ -502,6 +503,11 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 continue;
             }
 #pragma nv_diag_suppress 128   // (the EW > 1 instantiations never reach the generic chunk loop)
+            // FWD / DX: the next chunk streams out of TMEM while this one is converted and stored
+            constexpr bool PREFETCH = (OP != OP_DW) && !SPLIT;
+            const uint32_t acc_addr = tmem_base + ((q * 32u) << 16) + (buf * RB + rblk) * TILE_C;
+            uint32_t vnext[32];
+            if (PREFETCH) tmem_ld_32x32(acc_addr + cgrp * 32, vnext);
 #pragma unroll 1
             for (int c = (int)cgrp; c < TILE_C / 32; c += EW) {
                 uint32_t v[32];
@@ -510,8 +516,15 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     same = __shfl_sync(0xffffffffu, eqmask, c) & own;   // merge only among this warp's chunks
                     if (same & ((1u << c) - 1u)) continue;   // already merged into an earlier chunk
                 }
-                tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + (buf * RB + rblk) * TILE_C + c * 32, v);
-                tmem_ld_wait();
+                if (PREFETCH) {
+                    tmem_ld_wait_regs(vnext);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = vnext[j];
+                    if (c + EW < TILE_C / 32) tmem_ld_32x32(acc_addr + (c + EW) * 32, vnext);
+                } else {
+                    tmem_ld_32x32(acc_addr + c * 32, v);
+                    tmem_ld_wait();
+                }
                 if (SPLIT) {   // main + correction accumulators, added with round-to-nearest
                     uint32_t w[32];
                     tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + CORR_COL + c * 32, w);
