@@ -127,6 +127,28 @@ def torch_io_dtype(dtype: torch.dtype) -> int:
     raise TypeError(f"rzlinear_b200 supports float32 and bfloat16 activations, got {dtype}")
 
 
+class _on:
+    """Makes `device` current around a call.  Cheaper than torch.cuda.device() in the common case where it
+    already is (no device switch, no context-manager machinery): small problems are bound by host time."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx = device.index
+
+    def __enter__(self):
+        self.prev = torch.cuda.current_device()
+        if self.idx is not None and self.idx != self.prev:
+            torch.cuda.set_device(self.idx)
+        else:
+            self.idx = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.idx is not None:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
@@ -165,53 +187,53 @@ def hash_indices_device(pb: RzProblem, device) -> torch.Tensor:
     nk = -(-pb.K // pb.BK)
     nn = -(-pb.N // pb.BN)
     out = torch.empty((nk, nn), dtype=torch.int64, device=device)
-    with torch.cuda.device(out.device):
+    with _on(out.device):
         check(load().rz_hash_indices_device(ctypes.byref(pb), _ptr(out), _stream(out.device)))
     return out
 
 
 def shadow_refresh(pb: RzProblem, hashed: torch.Tensor, shadow: torch.Tensor) -> None:
     _require_cuda(hashed, shadow)
-    with torch.cuda.device(hashed.device):
+    with _on(hashed.device):
         check(load().rz_shadow_refresh(ctypes.byref(pb), _ptr(hashed), _ptr(shadow), _stream(hashed.device)))
 
 
 def forward(pb, x, hashed, shadow, bias, y) -> None:
     _require_cuda(x, hashed, shadow, bias, y)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         check(load().rz_linear_forward(ctypes.byref(pb), _ptr(x), _ptr(hashed), _ptr(shadow), _ptr(bias), _ptr(y),
                                        _stream(x.device)))
 
 
 def backward_input(pb, dy, hashed, shadow, dx) -> None:
     _require_cuda(dy, hashed, shadow, dx)
-    with torch.cuda.device(dy.device):
+    with _on(dy.device):
         check(load().rz_linear_backward_input(ctypes.byref(pb), _ptr(dy), _ptr(hashed), _ptr(shadow), _ptr(dx),
                                               _stream(dy.device)))
 
 
 def backward_weight(pb, x, dy, dh) -> None:
     _require_cuda(x, dy, dh)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         check(load().rz_linear_backward_weight(ctypes.byref(pb), _ptr(x), _ptr(dy), _ptr(dh), _stream(x.device)))
 
 
 def materialize(pb, hashed, w) -> None:
     _require_cuda(hashed, w)
-    with torch.cuda.device(hashed.device):
+    with _on(hashed.device):
         check(load().rz_linear_materialize(ctypes.byref(pb), _ptr(hashed), _ptr(w), _stream(hashed.device)))
 
 
 def grad_prepare(pb, dy, y, dym, bias_grad) -> None:
     """dym = dy where y > 0 (y may be None: no mask), bias_grad = column sums of the (masked) gradient (may be None)."""
     _require_cuda(dy, y, dym, bias_grad)
-    with torch.cuda.device(dy.device):
+    with _on(dy.device):
         check(load().rz_grad_prepare(ctypes.byref(pb), _ptr(dy), _ptr(y), _ptr(dym), _ptr(bias_grad), _stream(dy.device)))
 
 
 def sgd_step(pb, hashed, dh, lr, shadow) -> None:
     _require_cuda(hashed, dh, shadow)
-    with torch.cuda.device(hashed.device):
+    with _on(hashed.device):
         check(load().rz_sgd_step(ctypes.byref(pb), _ptr(hashed), _ptr(dh), ctypes.c_float(lr), _ptr(shadow),
                                  _stream(hashed.device)))
 
@@ -222,7 +244,7 @@ def sgd_momentum_step(pb, hashed, dh, velocity, lr, momentum, shadow) -> None:
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.POINTER(RzProblem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
                    ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]
-    with torch.cuda.device(hashed.device):
+    with _on(hashed.device):
         check(fn(ctypes.byref(pb), _ptr(hashed), _ptr(dh), _ptr(velocity), ctypes.c_float(lr), ctypes.c_float(momentum),
                  _ptr(shadow), _stream(hashed.device)))
 
@@ -240,7 +262,7 @@ def selftest_bounded_wait(limit_cycles: int, device="cuda") -> None:
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.c_int64, ctypes.c_void_p]
     dev = torch.device(device)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(fn(int(limit_cycles), _stream(dev)))
 
 
@@ -261,5 +283,5 @@ def forward_noalloc(pb, x, hashed, bias, y) -> None:
     fn = load().rz_linear_forward_noalloc
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.POINTER(RzProblem)] + [ctypes.c_void_p] * 5
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         check(fn(ctypes.byref(pb), _ptr(x), _ptr(hashed), _ptr(bias), _ptr(y), _stream(x.device)))

@@ -84,8 +84,16 @@ void rz_count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_orde
 
 int *rz_device_status_word()
 {
+    static std::atomic<int *> cached[64];   // per device: the address never changes while the module is loaded
+    int dev = 0;
+    const bool cacheable = cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64;
+    if (cacheable) {
+        int *q = cached[dev].load(std::memory_order_acquire);
+        if (q) return q;
+    }
     int *p = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_rz_status_word) != cudaSuccess) return nullptr;
+    if (cacheable) cached[dev].store(p, std::memory_order_release);
     return p;
 }
 

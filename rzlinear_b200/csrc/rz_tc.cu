@@ -35,6 +35,7 @@
 // Every mbarrier wait is bounded: a wait that runs out records a code in the device status word and
 // all roles leave their loops, the producer waits for its loads in flight, the MMA thread for its
 // MMAs, TMEM is freed and the kernel returns.
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -1094,9 +1095,20 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     auto kern = rz_tc_kernel<OP, TF32, CTAS, RB, SPLIT, NC, EW>;
     constexpr int SMEM_TOTAL = smem_total(OP, CTAS, RB, SPLIT, NC, EW);
     static_assert(SMEM_TOTAL <= SMEM_LIMIT, "shared memory budget");
-    int st = rz_record_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL),
-                            "set max dynamic shared memory");
+    // Per kernel variant and device, once: the shared-memory opt-in and (pairs) how many clusters fit the device.
+    // Both are properties of the variant, and asking the runtime again on every call costs several microseconds
+    // of host time, which is what small problems are bound by.
+    static std::atomic<int> ready[64];   // 0 = not set up, else resident blocks / pairs + 1
+    int dev = 0;
+    int st = rz_record_cuda(cudaGetDevice(&dev), "cudaGetDevice");
     if (st) return st;
+    const bool cacheable = dev >= 0 && dev < 64;
+    int known = cacheable ? ready[dev].load(std::memory_order_acquire) : 0;
+    if (!known) {
+        st = rz_record_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL),
+                            "set max dynamic shared memory");
+        if (st) return st;
+    }
 
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -1115,11 +1127,16 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         cfg.gridDim = dim3(2 * (unsigned)slots, 1, 1);
-        int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) == cudaSuccess && clusters > 0 && clusters < slots)
-            slots = clusters;
-        (void)cudaGetLastError();
+        if (known) {
+            slots = known - 1;
+        } else {
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) == cudaSuccess && clusters > 0 && clusters < slots)
+                slots = clusters;
+            (void)cudaGetLastError();
+        }
     }
+    if (!known && cacheable) ready[dev].store(slots + 1, std::memory_order_release);
 
     const uint32_t tiles = p.tiles_r * p.tiles_c;
     p.nsplit = plan.nsplit > 1 ? (uint32_t)plan.nsplit : 1u;
