@@ -102,6 +102,7 @@ struct TcParams {
     float *ws;                  // FWD / DX with a split contraction: fp32 partial sums [rows][cols]
     int *status;
     long long wait_limit;
+    uint32_t tma_store;         // FWD / DX: write the output with bulk tensor stores (0 = plain 16-byte stores)
 };
 
 __device__ __forceinline__ void wait_cycles(uint32_t bar, uint32_t parity, long long cycles)
@@ -113,7 +114,8 @@ __device__ __forceinline__ void wait_cycles(uint32_t bar, uint32_t parity, long 
 
 template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC, int EW>
 __global__ void __launch_bounds__(num_threads(RB, SPLIT, EW), 1)
-rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams p)
+rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+             const __grid_constant__ CUtensorMap mapC, const TcParams p)
 {
     constexpr int ES = TF32 ? 4 : 2;        // operand element size
     constexpr int EPR = 128 / ES;           // elements per 128-byte swizzle row
@@ -188,6 +190,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         fence_proxy_async();
         tma_prefetch_desc(&mapA);
         tma_prefetch_desc(&mapB);
+        if (OP != OP_DW) tma_prefetch_desc(&mapC);
     }
     if (warp == 1) {
         if (CTAS == 2) {
@@ -534,6 +537,11 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
                 }
                 const uint32_t col = tc * TILE_C + c * 32;
+                if (OP != OP_DW && p.tma_store && (partial || TF32 || !(c & 1))) {
+                    // the staging tile is about to be rewritten: the bulk store issued from it must have read it
+                    if (lane == 0) bulk_wait_group_read0();
+                    __syncwarp();
+                }
                 if (OP == OP_DW) {
                     float acc[32];
 #pragma unroll
@@ -639,7 +647,17 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                         }
                         *reinterpret_cast<uint4 *>(stage + lane * 128 + (((cbase + g) ^ (lane & 7)) * 16)) = u;
                     }
-                    if (TF32 || (c & 1)) {
+                    if ((TF32 || (c & 1)) && p.tma_store) {
+                        // one bulk tensor store per staged 32-row x 128-byte tile (the tile is in the 128-byte-swizzle
+                        // layout the store expects; rows and columns past the matrix edge are clipped by the unit)
+                        const uint32_t col_seg = TF32 ? col : col - 32;
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0 && rbase < p.rows && col_seg < p.cols) {
+                            tma_store_2d(&mapC, smem_u32(stage), (int32_t)col_seg, (int32_t)rbase);
+                            bulk_commit_group();
+                        }
+                    } else if (TF32 || (c & 1)) {
                         __syncwarp();
                         constexpr int EPC = TF32 ? 4 : 8;                 // elements per 16-byte chunk
                         const uint32_t col_seg = TF32 ? col : col - 32;   // first column of the staged 128-byte segment
@@ -664,6 +682,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 else mbar_arrive(bar_tempty + 8 * buf);
             }
         }
+        if (OP != OP_DW && lane == 0) bulk_wait_group0();   // bulk stores still in flight read this CTA's shared memory
     }
 
     else if (SPLIT) {
@@ -1069,7 +1088,8 @@ uint32_t dx_box_rows(const rz_problem *pb, const TcConfig &c)
 }
 
 template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC, int EW = 1>
-int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, const TcConfig &plan)
+int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC, TcParams &p,
+              const TcConfig &plan)
 {
     const rz_problem *pb = c.pb;
     constexpr int ES = TF32 ? 4 : 2;
@@ -1153,6 +1173,7 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.status = rz_device_status_word();
     if (!p.status) return rz_record_cuda(cudaErrorUnknown, "status word address");
     p.wait_limit = 2000000000ll;
+    p.tma_store = env_u32("RZ_TC_TMA_STORE", 1);
 
     // shared-memory descriptors (bytes)
     const uint32_t atom = KC * 128;
@@ -1186,7 +1207,7 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
                             "zero workspace");
         if (st) return st;
     }
-    st = rz_record_cuda(cudaLaunchKernelEx(&cfg, kern, mapA, mapB, p), "tcgen05 kernel launch");
+    st = rz_record_cuda(cudaLaunchKernelEx(&cfg, kern, mapA, mapB, mapC, p), "tcgen05 kernel launch");
     rz_count_launch(1);
     if (st) return st;
     st = rz_record_cuda(cudaGetLastError(), "tcgen05 kernel launch");
@@ -1209,35 +1230,36 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
 }
 
 template <int OP>
-int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, TcParams &p, const TcConfig &cfg)
+int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC, TcParams &p,
+                  const TcConfig &cfg)
 {
     const int prec = c.pb->precision;
     if (prec == RZ_PREC_FP32) {   // split precision: fp32 operands, three tf32 MMAs per product
-        if (cfg.ctas == 2) return launch_tc<OP, true, 2, 1, 1, 256>(c, mapA, mapB, p, cfg);
-        if (cfg.nc == 256) return launch_tc<OP, true, 1, 1, 1, 256>(c, mapA, mapB, p, cfg);
-        if (cfg.nc == 128) return launch_tc<OP, true, 1, 1, 1, 128>(c, mapA, mapB, p, cfg);
-        return launch_tc<OP, true, 1, 1, 1, 64>(c, mapA, mapB, p, cfg);
+        if (cfg.ctas == 2) return launch_tc<OP, true, 2, 1, 1, 256>(c, mapA, mapB, mapC, p, cfg);
+        if (cfg.nc == 256) return launch_tc<OP, true, 1, 1, 1, 256>(c, mapA, mapB, mapC, p, cfg);
+        if (cfg.nc == 128) return launch_tc<OP, true, 1, 1, 1, 128>(c, mapA, mapB, mapC, p, cfg);
+        return launch_tc<OP, true, 1, 1, 1, 64>(c, mapA, mapB, mapC, p, cfg);
     }
     const bool tf32 = prec == RZ_PREC_TF32;
     if (OP == OP_DW && cfg.ew == 4 && cfg.rb == 1) {   // scatter-bound weight gradient: sixteen epilogue warps
         constexpr int W = (OP == OP_DW) ? 4 : 1;       // (keeps the other operations from instantiating the variant)
         if (cfg.ctas == 2)
-            return tf32 ? launch_tc<OP, true, 2, 1, 0, 256, W>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 2, 1, 0, 256, W>(c, mapA, mapB, p, cfg);
+            return tf32 ? launch_tc<OP, true, 2, 1, 0, 256, W>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 2, 1, 0, 256, W>(c, mapA, mapB, mapC, p, cfg);
         if (cfg.nc == 256)
-            return tf32 ? launch_tc<OP, true, 1, 1, 0, 256, W>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 256, W>(c, mapA, mapB, p, cfg);
+            return tf32 ? launch_tc<OP, true, 1, 1, 0, 256, W>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 1, 1, 0, 256, W>(c, mapA, mapB, mapC, p, cfg);
         if (cfg.nc == 128)
-            return tf32 ? launch_tc<OP, true, 1, 1, 0, 128, W>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 128, W>(c, mapA, mapB, p, cfg);
-        return tf32 ? launch_tc<OP, true, 1, 1, 0, 64, W>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 64, W>(c, mapA, mapB, p, cfg);
+            return tf32 ? launch_tc<OP, true, 1, 1, 0, 128, W>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 1, 1, 0, 128, W>(c, mapA, mapB, mapC, p, cfg);
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 64, W>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 1, 1, 0, 64, W>(c, mapA, mapB, mapC, p, cfg);
     }
     if (cfg.ctas == 2 && cfg.rb == 2)
-        return tf32 ? launch_tc<OP, true, 2, 2, 0, 256>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 2, 2, 0, 256>(c, mapA, mapB, p, cfg);
+        return tf32 ? launch_tc<OP, true, 2, 2, 0, 256>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 2, 2, 0, 256>(c, mapA, mapB, mapC, p, cfg);
     if (cfg.ctas == 2)
-        return tf32 ? launch_tc<OP, true, 2, 1, 0, 256>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 2, 1, 0, 256>(c, mapA, mapB, p, cfg);
+        return tf32 ? launch_tc<OP, true, 2, 1, 0, 256>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 2, 1, 0, 256>(c, mapA, mapB, mapC, p, cfg);
     if (cfg.nc == 256)
-        return tf32 ? launch_tc<OP, true, 1, 1, 0, 256>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 256>(c, mapA, mapB, p, cfg);
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 256>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 1, 1, 0, 256>(c, mapA, mapB, mapC, p, cfg);
     if (cfg.nc == 128)
-        return tf32 ? launch_tc<OP, true, 1, 1, 0, 128>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 128>(c, mapA, mapB, p, cfg);
-    return tf32 ? launch_tc<OP, true, 1, 1, 0, 64>(c, mapA, mapB, p, cfg) : launch_tc<OP, false, 1, 1, 0, 64>(c, mapA, mapB, p, cfg);
+        return tf32 ? launch_tc<OP, true, 1, 1, 0, 128>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 1, 1, 0, 128>(c, mapA, mapB, mapC, p, cfg);
+    return tf32 ? launch_tc<OP, true, 1, 1, 0, 64>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 1, 1, 0, 64>(c, mapA, mapB, mapC, p, cfg);
 }
 
 // 2-D map over a row-major matrix [rows][cols] of the operand type
@@ -1355,7 +1377,11 @@ int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const
     p.bias = bias;
     p.out = Y;
     p.ws = workspace_of(pb, shadow, RZ_OP_FORWARD);
-    return launch_tc_any<OP_FWD>(c, mapA, mapB, p, choose_config(pb, RZ_OP_FORWARD));
+    // output map for the epilogue's bulk stores: 32-row x 128-byte boxes
+    CUtensorMap mapC;
+    st = map_matrix(&mapC, tf32, false, Y, pb->M, pb->N, g.epr, 32);
+    if (st) return st;
+    return launch_tc_any<OP_FWD>(c, mapA, mapB, mapC, p, choose_config(pb, RZ_OP_FORWARD));
 }
 
 int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shadow, void *dX)
@@ -1373,7 +1399,10 @@ int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shado
     memset(&p, 0, sizeof(p));
     p.out = dX;
     p.ws = workspace_of(pb, shadow, RZ_OP_BACKWARD_INPUT);
-    return launch_tc_any<OP_DX>(c, mapA, mapB, p, config);
+    CUtensorMap mapC;
+    st = map_matrix(&mapC, tf32, false, dX, pb->M, pb->K, g.epr, 32);
+    if (st) return st;
+    return launch_tc_any<OP_DX>(c, mapA, mapB, mapC, p, config);
 }
 
 int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, float *dH)
@@ -1389,5 +1418,5 @@ int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, f
     TcParams p;
     memset(&p, 0, sizeof(p));
     p.dH = dH;
-    return launch_tc_any<OP_DW>(c, mapA, mapB, p, choose_config(pb, RZ_OP_BACKWARD_WEIGHT));
+    return launch_tc_any<OP_DW>(c, mapA, mapB, mapA, p, choose_config(pb, RZ_OP_BACKWARD_WEIGHT));   // (no output map)
 }
