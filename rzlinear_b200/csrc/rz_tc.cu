@@ -10,8 +10,9 @@
 //           MMAs for both; the barriers that gate them live in the leader.
 // CTAS = 2, RB = 2: the pair owns a 512 x 256 block as two M = 256 MMAs per K-step that share B: each CTA
 //           stages 2 x 128 rows of A and 128 columns of B, i.e. 48 KB per 1024 tensor-clocks instead of
-//           32 KB per 512.  The kernels are bound by what an SM can pull from L2 (about 50 B/clk), so
-//           this is the fast configuration; it is used whenever the output has at least 512 rows.
+//           32 KB per 512.  The main loop is bound by operand bytes per flop moved through an SM (L2 -> SM
+//           reads of about 50 B/clk, and the shared-memory port that TMA writes and the MMAs' operand reads
+//           share), so this is the fast configuration; it is used whenever the output has at least 512 rows.
 // SPLIT = 1 (fp32 precision on the tensor cores, RB = 1 only): operands are fp32; four extra warps split every
 //           staged tile in shared memory into hi = the tf32-representable part and lo = x - hi, and each K-step
 //           issues hi*hi + hi*lo + lo*hi (three tf32 MMAs, fp32 accumulate): fp32-grade results (the dropped
@@ -20,7 +21,8 @@
 // one block overlaps the main loop of the next; with RB = 2 both halves are accumulators of one block.
 // Warp 0 produces (TMA loads into a ring of 128-byte-swizzled shared-memory tiles), warp 1 issues
 // tcgen05.mma, 4*RB epilogue warps drain TMEM: they scale/bias/convert and store (FWD, DX) or scatter-add
-// into the hashed gradient with warp-wide coalesced reductions (DW).
+// into the hashed gradient with warp-wide coalesced reductions (DW).  EW = 4 (DW, RB = 1): sixteen epilogue
+// warps for weight gradients of short contractions, whose scatter outlasts the main loop.
 //
 // The virtual weight is never materialised.  For every pipeline stage the producer warp computes
 // the hash-tile offsets in registers and TMA-loads the matching rows of the slice.  TMA needs a
@@ -50,7 +52,6 @@ namespace {
 constexpr int OP_FWD = 0, OP_DX = 1, OP_DW = 2;
 
 constexpr int TILE_R = 128;  // rows per CTA and accumulator (MMA M = 128 * CTAS)
-constexpr int TILE_C_MAX = 256;  // widest block (MMA N); narrower blocks (128, 64) serve small grids
 constexpr int A_BLOCK_BYTES = 16384;  // one 128-row block of A per stage
 constexpr int BATCH = 8;     // pipeline stages per hash batch of the producer warp
 constexpr int MAX_TPS = 8;   // B boxes per stage at most
