@@ -30,7 +30,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference/python")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout's python/ directory")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     from rz_linear import RzLinear
