@@ -1026,15 +1026,28 @@ TcConfig choose_config(const rz_problem *pb, int op)
             const int64_t need = (depth + 2047) / 2048;
             if (c.nsplit < need) c.nsplit = (int)need;
         }
-        // Ragged last wave (FWD / DX): the blocks left over after the full waves are split over the idle CTAs, so the
-        // tail costs 1/nsplit of a wave instead of a whole one; only those blocks go through the workspace.
+        // Ragged last wave: the blocks left over after the full waves are split along the contraction, so the tail costs
+        // ceil(tail * parts / slots) / parts of a wave instead of a whole one.  Every part pays the block's epilogue
+        // again (FWD / DX: fp32 reductions into the workspace, which only those blocks go through, plus the finalize
+        // launch; DW: its scatter, which it pays anyway), counted here in pipeline stages.
         const int64_t tail = items % slots;
-        if (!no_split && c.nsplit == 1 && op != RZ_OP_BACKWARD_WEIGHT && items > slots && tail > 0 && tail * 2 <= slots &&
-            stages >= 32) {
-            int64_t s2 = slots / tail, most = stages / 8;
-            if (s2 > most) s2 = most;
-            if (s2 >= 2) {
-                c.nsplit = (int)s2;
+        double tail_waves = 1.0;   // time of the last wave, in whole-contraction blocks
+        if (!no_split && c.nsplit == 1 && items > slots && tail > 0 && stages >= 32) {
+            const bool dw = op == RZ_OP_BACKWARD_WEIGHT;
+            const double per_part = dw ? (c.rb == 2 ? 19.0 : 4.0) : (c.rb == 2 ? 10.0 : 5.0);
+            const double whole = (double)stages + (dw ? per_part : 0.0);
+            int64_t best_parts = 1;
+            const int64_t most = stages / 8 < 16 ? stages / 8 : 16;
+            for (int64_t parts = 2; parts <= most; ++parts) {
+                const double t = (double)((tail * parts + slots - 1) / slots) * ((double)stages / (double)parts + per_part) / whole +
+                                 (dw ? 0.0 : 0.05);
+                if (t < tail_waves - 0.04) {
+                    tail_waves = t;
+                    best_parts = parts;
+                }
+            }
+            if (best_parts > 1) {
+                c.nsplit = (int)best_parts;
                 c.n_main = (int)(items - tail);
             }
         }
@@ -1055,7 +1068,7 @@ TcConfig choose_config(const rz_problem *pb, int op)
         } else if (c.n_main == 0) {
             waves = (double)((items * c.nsplit + slots - 1) / slots) / c.nsplit + 0.1;
         } else {
-            waves = (double)(c.n_main / slots) + (double)((tail * c.nsplit + slots - 1) / slots) / c.nsplit + 0.1;
+            waves = (double)(c.n_main / slots) + tail_waves;
         }
         const double occupancy = ((double)items / (double)slots) / waves;
         // useful fraction of the block (ragged last row block)
@@ -1099,6 +1112,7 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     constexpr int PAIR_R = TILE_R * CTAS;
     constexpr int ITEM_R = PAIR_R * RB;
     constexpr int NTHREADS = num_threads(RB, SPLIT, EW);
+    constexpr int STAGES_HOST = num_stages(OP, CTAS, RB, SPLIT, NC, EW);
     p.hash = c.hash;
     p.M = (uint32_t)pb->M;
     p.K = (uint32_t)pb->K;
@@ -1199,6 +1213,10 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (a_major << 15) | (b_major << 16) | ((uint32_t)(NC >> 3) << 17) |
               ((uint32_t)(PAIR_R >> 4) << 24);
 
+    static const bool verbose = env_u32("RZ_TC_VERBOSE", 0) != 0;   // bring-up aid: one line per launch on stderr
+    if (verbose)
+        fprintf(stderr, "rz_tc op %d tf32 %d block (%d,%d,%d) ew %d stages %d: %u blocks, %u whole + %u x %u parts, %d slots\n", OP,
+                (int)TF32, CTAS, RB, NC, EW, STAGES_HOST, tiles, p.n_main, tiles - p.n_main, p.nsplit, slots);
     const uint32_t blocks = p.total_items < (uint32_t)slots ? p.total_items : (uint32_t)slots;
     cfg.gridDim = dim3(blocks * CTAS, 1, 1);
     const bool partial = OP != OP_DW && p.nsplit > 1;
