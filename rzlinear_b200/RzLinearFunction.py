@@ -38,6 +38,16 @@ def _unpack(random_numbers):
     return [int(v) for v in random_numbers.tolist()]
 
 
+def _compute_view(t: torch.Tensor) -> torch.Tensor:
+    """Contiguous activations in a dtype the kernels take.  float32 and bfloat16 pass through; anything else
+    (float16, float64: the reference accepts whatever Triton does) is computed in float32 and cast back."""
+    if t.dtype in (torch.float32, torch.bfloat16):
+        return t.contiguous()
+    if not t.is_floating_point():
+        raise TypeError(f"RzLinear takes floating-point activations, got {t.dtype}")
+    return t.float().contiguous()
+
+
 class RzLinearFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input: torch.Tensor, hashed_weight: torch.Tensor, random_numbers: torch.Tensor,
@@ -61,7 +71,7 @@ class RzLinearFunction(torch.autograd.Function):
         R = _unpack(random_numbers)
         M, K, N, H = input.shape[0], input.shape[1], output_dim, hashed_weight.shape[0]
         allow_tf32 = controls['triton_allow_tf32']
-        x = input.contiguous()
+        x = _compute_view(input)
         hashed = launchers._hashed_f32(hashed_weight)
         flags = _lib.FLAG_RELU if cfg.relu else 0
         pb = launchers.make_problem(M, K, N, H, R, cfg.block_size_k, cfg.block_size_n, x.dtype, allow_tf32,
@@ -71,6 +81,7 @@ class RzLinearFunction(torch.autograd.Function):
         b = None if bias is None else bias.detach().float().contiguous()
         _lib.forward(pb, x, hashed, shadow, b, out)
 
+        # (the saved output keeps the compute dtype: the backward masks with it)
         ctx.save_for_backward(input, hashed_weight, random_numbers, out if cfg.relu else None)
         ctx.shadow = shadow  # the backward reads the weights the forward saw
         ctx.output_dim = output_dim
@@ -79,7 +90,7 @@ class RzLinearFunction(torch.autograd.Function):
         ctx.config = cfg
         ctx.allow_tf32 = allow_tf32
         ctx.has_bias = bias is not None
-        return out
+        return out if out.dtype == input.dtype else out.to(input.dtype)
 
     @staticmethod
     def backward(ctx, grad):
@@ -87,8 +98,8 @@ class RzLinearFunction(torch.autograd.Function):
         cfg = ctx.config
         R = _unpack(random_numbers)
         M, K, N, H = input.shape[0], input.shape[1], ctx.output_dim, hashed_weight.shape[0]
-        grad = grad.contiguous()
-        x = input.contiguous()
+        x = _compute_view(input)
+        grad = grad.contiguous() if grad.dtype == x.dtype else grad.to(x.dtype).contiguous()
         hashed = launchers._hashed_f32(hashed_weight)
         pb = launchers.make_problem(M, K, N, H, R, cfg.block_size_k, cfg.block_size_n, x.dtype, ctx.allow_tf32,
                                     ctx.init_factor, cfg.hash_mode)
@@ -96,8 +107,6 @@ class RzLinearFunction(torch.autograd.Function):
         # one pass over the incoming gradient: ReLU mask from the saved output and the bias gradient (column sums)
         want_bias = ctx.has_bias and ctx.needs_input_grad[7]
         if cfg.relu or want_bias:
-            if grad.dtype != x.dtype:
-                grad = grad.to(x.dtype)
             masked = torch.empty_like(grad) if cfg.relu else None
             bias_grad = torch.empty((N,), device=x.device, dtype=torch.float32) if want_bias else None
             _lib.grad_prepare(pb, grad, out if cfg.relu else None, masked, bias_grad)
@@ -106,6 +115,8 @@ class RzLinearFunction(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             input_grad = torch.empty((M, K), device=x.device, dtype=x.dtype)
             _lib.backward_input(pb, grad, hashed, ctx.shadow, input_grad)
+            if input_grad.dtype != input.dtype:
+                input_grad = input_grad.to(input.dtype)
         if ctx.needs_input_grad[1]:
             dh = torch.empty((H,), device=x.device, dtype=torch.float32)
             _lib.backward_weight(pb, x, grad, dh)

@@ -228,6 +228,29 @@ def test_module_matches_reference_fixture(golden_dir):
     assert o.rel_l2(rz._bias.grad.cpu().numpy(), d["dbias"]) < TOL_FP32
 
 
+def test_module_accepts_float16_activations():
+    # float16 is not a kernel dtype: the layer computes in float32 (tf32 allowed by default) and casts back
+    from rzlinear_b200 import RzLinear
+    torch.manual_seed(3)
+    hw = torch.nn.Parameter((torch.rand(12288) * 2 - 1) / 128 ** 0.5)   # (the default initialisation is far outside float16's range)
+    rz = RzLinear(128, 192, hashed_weight=hw, seed=5, bias=True).to(DEV)
+    x16 = torch.randn(40, 128, device=DEV).half().requires_grad_(True)
+    y16 = rz(x16)
+    assert y16.dtype == torch.float16 and y16.shape == (40, 192)
+    y16.float().pow(2).sum().backward()
+    g16, gh16 = x16.grad.clone(), rz._hashed_weight.grad.clone()
+    assert g16.dtype == torch.float16
+    rz._hashed_weight.grad = None
+    x32 = x16.detach().float().requires_grad_(True)
+    y32 = rz(x32)
+    y32.pow(2).sum().backward()
+    errs = (o.rel_l2(y16.detach().float().cpu().numpy(), y32.detach().cpu().numpy()),
+            o.rel_l2(g16.float().cpu().numpy(), x32.grad.cpu().numpy()),
+            o.rel_l2(gh16.cpu().numpy(), rz._hashed_weight.grad.cpu().numpy()))
+    # float16 rounding of the output and of the incoming gradient (2^-11 per element) is all that separates the two runs
+    assert max(errs) < 2e-3, errs
+
+
 def test_module_shape_smoke_like_reference_test_module():
     from rzlinear_b200 import RzLinear
     rz = RzLinear(input_dim=1024, output_dim=1024).to(DEV)

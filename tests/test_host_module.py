@@ -62,6 +62,8 @@ def test_cpu_tensors_are_rejected_not_emulated():
     with pytest.raises(AssertionError):
         small(torch.randn(4, 64))
     with pytest.raises(TypeError):
+        RzLinear(64, 128, compress_ratio=0.5)(torch.ones(4, 64, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="CUDA"):      # float16 is computed in float32, still only on the GPU
         RzLinear(64, 128, compress_ratio=0.5)(torch.randn(4, 64).half())
 
 
