@@ -76,7 +76,7 @@ class RzLinearFunction(torch.autograd.Function):
         flags = _lib.FLAG_RELU if cfg.relu else 0
         pb = launchers.make_problem(M, K, N, H, R, cfg.block_size_k, cfg.block_size_n, x.dtype, allow_tf32,
                                     init_factor, cfg.hash_mode, flags)
-        shadow = launchers.alloc_shadow(pb, hashed)
+        shadow = launchers.cached_shadow(pb, hashed_weight, hashed)   # refreshed only when the weights changed
         out = torch.empty((M, N), device=x.device, dtype=x.dtype)
         b = None if bias is None else bias.detach().float().contiguous()
         _lib.forward(pb, x, hashed, shadow, b, out)

@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "librzlinear_b200.so")
 
 # enum values of include/rzlinear_b200.h
 RZ_OK = 0
+RZ_ERR_CUDA, RZ_ERR_PIPELINE, RZ_ERR_TOO_LARGE, RZ_ERR_SCRATCH = -7, -8, -10, -11
 HASH_SINGLE, HASH_TWO_LEVEL = 0, 1
 F32, BF16 = 0, 1
 PREC_FP32, PREC_TF32, PREC_BF16 = 0, 1, 2
@@ -28,7 +29,8 @@ EXPORTS = [
     "rz_hash_indices_device", "rz_plan", "rz_shadow_bytes", "rz_shadow_refresh",
     "rz_linear_forward", "rz_linear_backward_input", "rz_linear_backward_weight",
     "rz_linear_materialize", "rz_sgd_step", "rz_device_status", "rz_launch_count",
-    "rz_selftest_bounded_wait", "rz_sgd_momentum_step", "rz_grad_prepare",
+    "rz_selftest_bounded_wait", "rz_sgd_momentum_step", "rz_grad_prepare", "rz_linear_forward_noalloc",
+    "rz_reload_env",
 ]
 
 
@@ -39,7 +41,7 @@ class RzProblem(ctypes.Structure):
         ("hash_mode", ctypes.c_int32), ("io_dtype", ctypes.c_int32),
         ("precision", ctypes.c_int32), ("flags", ctypes.c_int32),
         ("R", ctypes.c_int64 * 8),
-        ("alpha", ctypes.c_float), ("reserved", ctypes.c_int32),
+        ("alpha", ctypes.c_float), ("sm_reserve", ctypes.c_int32),
     ]
 
 
@@ -78,18 +80,23 @@ def load() -> ctypes.CDLL:
         lib.rz_shadow_bytes.restype = ctypes.c_size_t
         lib.rz_shadow_bytes.argtypes = [pbp]
         lib.rz_shadow_refresh.argtypes = [pbp, vp, vp, vp]
-        lib.rz_linear_forward.argtypes = [pbp, vp, vp, vp, vp, vp, vp]
-        lib.rz_linear_backward_input.argtypes = [pbp, vp, vp, vp, vp, vp]
+        lib.rz_linear_forward.argtypes = [pbp, vp, vp, vp, ctypes.c_size_t, vp, vp, vp]
+        lib.rz_linear_backward_input.argtypes = [pbp, vp, vp, vp, ctypes.c_size_t, vp, vp]
         lib.rz_linear_backward_weight.argtypes = [pbp, vp, vp, vp, vp]
         lib.rz_linear_materialize.argtypes = [pbp, vp, vp, vp]
         lib.rz_grad_prepare.argtypes = [pbp, vp, vp, vp, vp, vp]
         lib.rz_grad_prepare.restype = ctypes.c_int
         lib.rz_sgd_step.argtypes = [pbp, vp, vp, ctypes.c_float, vp, vp]
+        lib.rz_sgd_momentum_step.argtypes = [pbp, vp, vp, vp, ctypes.c_float, ctypes.c_float, vp, vp]
+        lib.rz_selftest_bounded_wait.argtypes = [ctypes.c_int64, vp]
+        lib.rz_linear_forward_noalloc.argtypes = [pbp, vp, vp, vp, vp, vp]
+        lib.rz_reload_env.restype = None
         lib.rz_device_status.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         lib.rz_launch_count.restype = ctypes.c_uint64
         for name in ("rz_hash_indices_host", "rz_hash_indices_device", "rz_plan", "rz_shadow_refresh",
                      "rz_linear_forward", "rz_linear_backward_input", "rz_linear_backward_weight",
-                     "rz_linear_materialize", "rz_sgd_step", "rz_device_status"):
+                     "rz_linear_materialize", "rz_sgd_step", "rz_device_status", "rz_sgd_momentum_step",
+                     "rz_selftest_bounded_wait", "rz_linear_forward_noalloc"):
             getattr(lib, name).restype = ctypes.c_int
         _lib = lib
     return _lib
@@ -100,12 +107,12 @@ def check(status: int) -> None:
         return
     lib = load()
     msg = lib.rz_status_string(status).decode()
-    if status == -7:
+    if status == RZ_ERR_CUDA:
         msg += ": " + lib.rz_last_cuda_error().decode()
     raise RzLinearError(status, msg)
 
 
-def make_problem(M, K, N, H, BK, BN, R, hash_mode, io_dtype, precision, alpha=1.0, flags=0) -> RzProblem:
+def make_problem(M, K, N, H, BK, BN, R, hash_mode, io_dtype, precision, alpha=1.0, flags=0, sm_reserve=0) -> RzProblem:
     pb = RzProblem()
     pb.M, pb.K, pb.N, pb.H = int(M), int(K), int(N), int(H)
     pb.BK, pb.BN = int(BK), int(BN)
@@ -116,7 +123,17 @@ def make_problem(M, K, N, H, BK, BN, R, hash_mode, io_dtype, precision, alpha=1.
     for i, v in enumerate(R):
         pb.R[i] = v
     pb.alpha = float(alpha)
+    pb.sm_reserve = int(sm_reserve)
     return pb
+
+
+def with_fields(pb: RzProblem, **fields) -> RzProblem:
+    """A copy of `pb` with some fields replaced (M, flags, sm_reserve, ...)."""
+    out = RzProblem()
+    ctypes.memmove(ctypes.byref(out), ctypes.byref(pb), ctypes.sizeof(RzProblem))
+    for name, value in fields.items():
+        setattr(out, name, value)
+    return out
 
 
 def torch_io_dtype(dtype: torch.dtype) -> int:
@@ -198,18 +215,23 @@ def shadow_refresh(pb: RzProblem, hashed: torch.Tensor, shadow: torch.Tensor) ->
         check(load().rz_shadow_refresh(ctypes.byref(pb), _ptr(hashed), _ptr(shadow), _stream(hashed.device)))
 
 
+def _nbytes(t) -> int:
+    return 0 if t is None else t.numel() * t.element_size()
+
+
 def forward(pb, x, hashed, shadow, bias, y) -> None:
+    """Raises RzLinearError(RZ_ERR_SCRATCH) when `shadow` is smaller than shadow_bytes(pb)."""
     _require_cuda(x, hashed, shadow, bias, y)
     with _on(x.device):
-        check(load().rz_linear_forward(ctypes.byref(pb), _ptr(x), _ptr(hashed), _ptr(shadow), _ptr(bias), _ptr(y),
-                                       _stream(x.device)))
+        check(load().rz_linear_forward(ctypes.byref(pb), _ptr(x), _ptr(hashed), _ptr(shadow), _nbytes(shadow), _ptr(bias),
+                                       _ptr(y), _stream(x.device)))
 
 
 def backward_input(pb, dy, hashed, shadow, dx) -> None:
     _require_cuda(dy, hashed, shadow, dx)
     with _on(dy.device):
-        check(load().rz_linear_backward_input(ctypes.byref(pb), _ptr(dy), _ptr(hashed), _ptr(shadow), _ptr(dx),
-                                              _stream(dy.device)))
+        check(load().rz_linear_backward_input(ctypes.byref(pb), _ptr(dy), _ptr(hashed), _ptr(shadow), _nbytes(shadow),
+                                              _ptr(dx), _stream(dy.device)))
 
 
 def backward_weight(pb, x, dy, dh) -> None:
@@ -241,9 +263,6 @@ def sgd_step(pb, hashed, dh, lr, shadow) -> None:
 def sgd_momentum_step(pb, hashed, dh, velocity, lr, momentum, shadow) -> None:
     _require_cuda(hashed, dh, velocity, shadow)
     fn = load().rz_sgd_momentum_step
-    fn.restype = ctypes.c_int
-    fn.argtypes = [ctypes.POINTER(RzProblem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
-                   ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]
     with _on(hashed.device):
         check(fn(ctypes.byref(pb), _ptr(hashed), _ptr(dh), _ptr(velocity), ctypes.c_float(lr), ctypes.c_float(momentum),
                  _ptr(shadow), _stream(hashed.device)))
@@ -259,8 +278,6 @@ def device_status():
 def selftest_bounded_wait(limit_cycles: int, device="cuda") -> None:
     """Launch the bounded-wait self-test kernel; read the outcome with device_status()."""
     fn = load().rz_selftest_bounded_wait
-    fn.restype = ctypes.c_int
-    fn.argtypes = [ctypes.c_int64, ctypes.c_void_p]
     dev = torch.device(device)
     with _on(dev):
         check(fn(int(limit_cycles), _stream(dev)))
@@ -270,6 +287,11 @@ def launch_count() -> int:
     return int(load().rz_launch_count())
 
 
+def reload_env() -> None:
+    """Make the library read its RZ_TC_* bring-up knobs from the environment again."""
+    load().rz_reload_env()
+
+
 NOALLOC_SCRATCH_BYTES = 16 << 20
 
 
@@ -277,11 +299,9 @@ def forward_noalloc(pb, x, hashed, bias, y) -> None:
     """rz_linear_forward_noalloc: forward pass whose scratch is a fixed array inside the library.
 
     For hosts that cannot allocate device memory when they call (see include/rzlinear_b200.h for who
-    that is and for the limits: shadow <= NOALLOC_SCRATCH_BYTES, one shared array per device, calls
+    that is and for the limits: shifted copies <= NOALLOC_SCRATCH_BYTES, one shared array per device, calls
     that overlap on the GPU race, first call per device before any stream capture)."""
     _require_cuda(x, hashed, bias, y)
     fn = load().rz_linear_forward_noalloc
-    fn.restype = ctypes.c_int
-    fn.argtypes = [ctypes.POINTER(RzProblem)] + [ctypes.c_void_p] * 5
     with _on(x.device):
         check(fn(ctypes.byref(pb), _ptr(x), _ptr(hashed), _ptr(bias), _ptr(y), _stream(x.device)))

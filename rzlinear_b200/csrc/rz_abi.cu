@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "rz_common.h"
 
@@ -11,8 +12,26 @@ namespace {
 thread_local char g_cuda_error[256] = "";
 std::atomic<uint64_t> g_launches{0};
 
-// Device-side status word: 0, or (wait code << 8 | 1) once a bounded wait gave up.
+// Device-side status word: 0, or (wait code << 8 | 1) once a bounded wait gave up.  Sticky until rz_device_status().
 __device__ int g_rz_status_word = 0;
+// Epoch of the launch whose wait gave up last: tells that launch's other waiters to leave.
+__device__ unsigned g_rz_abort_epoch = 0;
+
+// Host copy of the status words, one int per device index, in a page of this library that is registered as
+// mapped pinned memory the first time a tensor-core launch is prepared: a kernel whose wait gives up stores its
+// code here too, and the host reads it (a plain load, no synchronisation) before it launches anything else.
+constexpr int RZ_MAX_DEVICES = 64;
+alignas(4096) int g_host_status[1024];
+std::once_flag g_host_once;
+bool g_host_registered = false;
+
+struct DeviceAddrs {
+    std::atomic<int *> status{nullptr};
+    std::atomic<unsigned *> abort_word{nullptr};
+    std::atomic<int *> host{nullptr};
+};
+DeviceAddrs g_addrs[RZ_MAX_DEVICES];
+std::atomic<unsigned> g_epoch{0};
 
 int validate(const rz_problem *pb)
 {
@@ -31,6 +50,7 @@ int validate(const rz_problem *pb)
         return RZ_ERR_DTYPE;
     if (pb->precision == RZ_PREC_TF32 && pb->io_dtype != RZ_F32) return RZ_ERR_DTYPE;
     if (pb->precision == RZ_PREC_BF16 && pb->io_dtype != RZ_BF16) return RZ_ERR_DTYPE;
+    if (pb->sm_reserve < 0 || pb->sm_reserve > 1024) return RZ_ERR_SHAPE;
     return RZ_OK;
 }
 
@@ -82,19 +102,60 @@ int rz_record_cuda(cudaError_t e, const char *what)
 
 void rz_count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
-int *rz_device_status_word()
+int rz_wait_context(RzWaitCtx *w, long long limit_cycles)
 {
-    static std::atomic<int *> cached[64];   // per device: the address never changes while the module is loaded
     int dev = 0;
-    const bool cacheable = cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64;
-    if (cacheable) {
-        int *q = cached[dev].load(std::memory_order_acquire);
-        if (q) return q;
+    int st = rz_record_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (st) return st;
+    if (dev < 0 || dev >= RZ_MAX_DEVICES) return RZ_ERR_UNSUPPORTED;
+    DeviceAddrs &a = g_addrs[dev];
+    int *status = a.status.load(std::memory_order_acquire);
+    if (!status) {   // first launch on this device: the addresses never change while the module is loaded
+        unsigned *abort_word = nullptr;
+        st = rz_record_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_rz_status_word), "status word address");
+        if (st) return st;
+        st = rz_record_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(&abort_word), g_rz_abort_epoch), "abort word address");
+        if (st) return st;
+        std::call_once(g_host_once, [] {
+            g_host_registered = cudaHostRegister(g_host_status, sizeof(g_host_status),
+                                                 cudaHostRegisterPortable | cudaHostRegisterMapped) == cudaSuccess;
+            if (!g_host_registered) (void)cudaGetLastError();   // no host copy: rz_device_status() is the only report
+        });
+        int *host_dev = nullptr;
+        if (g_host_registered &&
+            cudaHostGetDevicePointer(reinterpret_cast<void **>(&host_dev), g_host_status + dev, 0) != cudaSuccess) {
+            host_dev = nullptr;
+            (void)cudaGetLastError();
+        }
+        a.host.store(host_dev, std::memory_order_relaxed);
+        a.abort_word.store(abort_word, std::memory_order_relaxed);
+        a.status.store(status, std::memory_order_release);
     }
-    int *p = nullptr;
-    if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_rz_status_word) != cudaSuccess) return nullptr;
-    if (cacheable) cached[dev].store(p, std::memory_order_release);
-    return p;
+    w->status = status;
+    w->abort_word = a.abort_word.load(std::memory_order_relaxed);
+    w->host_status = a.host.load(std::memory_order_relaxed);
+    w->limit_cycles = limit_cycles;
+    if (w->host_status && *reinterpret_cast<volatile int *>(&g_host_status[dev]) != 0) return RZ_ERR_PIPELINE;
+    unsigned e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+    if (e == 0) e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;   // 0 is the abort word's idle value
+    w->epoch = e;
+    return RZ_OK;
+}
+
+int rz_forward_with_scratch(const rz_problem *pb, const void *X, const float *hashed, void *shadow, size_t shadow_bytes,
+                            const float *bias, void *Y, void *stream, bool copies_suffice)
+{
+    int st = validate(pb);
+    if (st) return st;
+    if (!X || !hashed || !Y) return RZ_ERR_NULL;
+    RzLaunchCtx c = make_ctx(pb, stream);
+    if (use_tc(pb, RZ_OP_FORWARD)) {
+        if (!shadow) return RZ_ERR_NULL;
+        if (!aligned16(X) || !aligned16(Y) || (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
+        if (shadow_bytes < (copies_suffice ? rz_tc_copies_bytes(pb) : rz_tc_shadow_bytes(pb))) return RZ_ERR_SCRATCH;
+        return rz_tc_forward(c, X, shadow, shadow_bytes, bias, Y);
+    }
+    return rz_simt_forward(c, X, hashed, bias, Y);
 }
 
 extern "C" {
@@ -112,9 +173,10 @@ const char *rz_status_string(int status)
     case RZ_ERR_ALIGN: return "pointer not 16-byte aligned";
     case RZ_ERR_HASH_PARAM: return "bad hash parameters (prime <= 0, negative or >= 2^31 random number, unknown mode)";
     case RZ_ERR_CUDA: return "CUDA call failed";
-    case RZ_ERR_PIPELINE: return "device pipeline wait timed out";
+    case RZ_ERR_PIPELINE: return "device pipeline wait timed out (results since then are invalid; rz_device_status() clears it)";
     case RZ_ERR_UNSUPPORTED: return "problem not supported on the requested path";
     case RZ_ERR_TOO_LARGE: return "size exceeds the capacity of this entry point";
+    case RZ_ERR_SCRATCH: return "scratch buffer smaller than rz_shadow_bytes() of this problem";
     default: return "unknown status";
     }
 }
@@ -167,22 +229,13 @@ int rz_shadow_refresh(const rz_problem *pb, const float *hashed, void *shadow, v
     return rz_tc_shadow_refresh(make_ctx(pb, stream), hashed, shadow);
 }
 
-int rz_linear_forward(const rz_problem *pb, const void *X, const float *hashed, const void *shadow,
+int rz_linear_forward(const rz_problem *pb, const void *X, const float *hashed, void *shadow, size_t shadow_bytes,
                       const float *bias, void *Y, void *stream)
 {
-    int st = validate(pb);
-    if (st) return st;
-    if (!X || !hashed || !Y) return RZ_ERR_NULL;
-    RzLaunchCtx c = make_ctx(pb, stream);
-    if (use_tc(pb, RZ_OP_FORWARD)) {
-        if (!shadow) return RZ_ERR_NULL;
-        if (!aligned16(X) || !aligned16(Y) || (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
-        return rz_tc_forward(c, X, shadow, bias, Y);
-    }
-    return rz_simt_forward(c, X, hashed, bias, Y);
+    return rz_forward_with_scratch(pb, X, hashed, shadow, shadow_bytes, bias, Y, stream, false);
 }
 
-int rz_linear_backward_input(const rz_problem *pb, const void *dY, const float *hashed, const void *shadow,
+int rz_linear_backward_input(const rz_problem *pb, const void *dY, const float *hashed, void *shadow, size_t shadow_bytes,
                              void *dX, void *stream)
 {
     int st = validate(pb);
@@ -192,7 +245,8 @@ int rz_linear_backward_input(const rz_problem *pb, const void *dY, const float *
     if (use_tc(pb, RZ_OP_BACKWARD_INPUT)) {
         if (!shadow) return RZ_ERR_NULL;
         if (!aligned16(dY) || !aligned16(dX) || (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
-        return rz_tc_backward_input(c, dY, shadow, dX);
+        if (shadow_bytes < rz_tc_shadow_bytes(pb)) return RZ_ERR_SCRATCH;
+        return rz_tc_backward_input(c, dY, shadow, shadow_bytes, dX);
     }
     return rz_simt_backward_input(c, dY, hashed, dX);
 }
@@ -238,7 +292,7 @@ int rz_sgd_step(const rz_problem *pb, float *hashed, const float *dH, float lr, 
     if (!aligned16(hashed) || !aligned16(dH)) return RZ_ERR_ALIGN;
     if (shadow && rz_shadow_bytes(pb) == 0) shadow = nullptr;
     if (shadow && (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
-    return rz_tc_sgd_step(make_ctx(pb, stream), hashed, dH, lr, shadow);
+    return rz_tc_sgd_step(make_ctx(pb, stream), hashed, dH, nullptr, lr, 0.f, shadow);
 }
 
 int rz_sgd_momentum_step(const rz_problem *pb, float *hashed, const float *dH, float *velocity, float lr, float momentum,
@@ -250,7 +304,7 @@ int rz_sgd_momentum_step(const rz_problem *pb, float *hashed, const float *dH, f
     if (!aligned16(hashed) || !aligned16(dH) || !aligned16(velocity)) return RZ_ERR_ALIGN;
     if (shadow && rz_shadow_bytes(pb) == 0) shadow = nullptr;
     if (shadow && (reinterpret_cast<uintptr_t>(shadow) & 255u)) return RZ_ERR_ALIGN;
-    return rz_tc_sgd_momentum_step(make_ctx(pb, stream), hashed, dH, velocity, lr, momentum, shadow);
+    return rz_tc_sgd_step(make_ctx(pb, stream), hashed, dH, velocity, lr, momentum, shadow);
 }
 
 int rz_device_status(int *out, int *detail)
@@ -266,6 +320,9 @@ int rz_device_status(int *out, int *detail)
         st = rz_record_cuda(cudaMemcpyToSymbol(g_rz_status_word, &zero, sizeof(int)), "clear status word");
         if (st) return st;
     }
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < RZ_MAX_DEVICES)
+        *reinterpret_cast<volatile int *>(&g_host_status[dev]) = 0;   // the device is idle: no kernel can be writing it
     *out = word ? RZ_ERR_PIPELINE : RZ_OK;
     if (detail) *detail = word >> 8;
     return RZ_OK;
@@ -278,5 +335,7 @@ int rz_selftest_bounded_wait(int64_t limit_cycles, void *stream)
 }
 
 uint64_t rz_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+void rz_reload_env(void) { rz_tc_reload_env(); }
 
 }  // extern "C"

@@ -18,6 +18,21 @@ enum RzWaitCode {
     RZ_WAIT_SELFTEST = 6
 };
 
+// Where a device-side bounded wait reports that it gave up (filled by rz_wait_context):
+//   status      sticky device word, read and cleared by rz_device_status();
+//   host_status host-mapped copy of it (may be NULL) that the host looks at, without synchronising, before
+//               every tensor-core launch, so that work after a failed kernel is refused instead of continuing
+//               on partial results;
+//   abort_word / epoch  tell the other waiters of the SAME launch to leave their loops; a launch reacts only
+//               to its own epoch, so a word left behind by an earlier launch never stops a later one.
+struct RzWaitCtx {
+    int *status;
+    int *host_status;
+    unsigned *abort_word;
+    unsigned epoch;
+    long long limit_cycles;
+};
+
 struct RzLaunchCtx {
     const rz_problem *pb;
     RzHash hash;
@@ -27,7 +42,14 @@ struct RzLaunchCtx {
 // host helpers (rz_abi.cu)
 int rz_record_cuda(cudaError_t e, const char *what);
 void rz_count_launch(int n);
-int *rz_device_status_word();  // device address of the status word of the current device
+// Fills `w` for a launch on the current device (fresh epoch).  RZ_ERR_PIPELINE when an earlier kernel on this
+// device reported a wait that gave up and rz_device_status() has not been called since.
+int rz_wait_context(RzWaitCtx *w, long long limit_cycles);
+
+// rz_linear_forward with a say on the scratch: `copies_suffice` lets a scratch that holds the shifted copies but not
+// the split-contraction workspace through (the launch then runs whole contractions per block).
+int rz_forward_with_scratch(const rz_problem *pb, const void *X, const float *hashed, void *shadow, size_t shadow_bytes,
+                            const float *bias, void *Y, void *stream, bool copies_suffice);
 
 // SIMT family (rz_simt.cu)
 int rz_simt_forward(const RzLaunchCtx &c, const void *X, const float *hashed, const float *bias, void *Y);
@@ -39,12 +61,16 @@ int rz_simt_hash_indices(const RzLaunchCtx &c, int64_t *out);
 
 // tcgen05 family (rz_tc.cu)
 bool rz_tc_supported(const rz_problem *pb, int op);
-size_t rz_tc_shadow_bytes(const rz_problem *pb);
+size_t rz_tc_shadow_bytes(const rz_problem *pb);          // shifted copies + workspace
+size_t rz_tc_copies_bytes(const rz_problem *pb);          // the shifted copies alone
+bool rz_tc_needs_workspace(const rz_problem *pb, int op); // the launch cannot run without its workspace (fp32 precision, long contraction)
+void rz_tc_reload_env();
 int rz_tc_shadow_refresh(const RzLaunchCtx &c, const float *hashed, void *shadow);
-int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float lr, void *shadow);
-int rz_tc_sgd_momentum_step(const RzLaunchCtx &c, float *hashed, const float *dH, float *velocity, float lr, float momentum,
-                            void *shadow);
-int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const float *bias, void *Y);
-int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shadow, void *dX);
+// velocity == NULL: plain SGD.  shadow == NULL: the hashed array alone is updated.
+int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float *velocity, float lr, float momentum, void *shadow);
+// `shadow_bytes`: size of the caller's scratch.  When it holds the copies but not the workspace the launch runs every
+// block's whole contraction (no workspace needed) unless rz_tc_needs_workspace().
+int rz_tc_forward(const RzLaunchCtx &c, const void *X, void *shadow, size_t shadow_bytes, const float *bias, void *Y);
+int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, void *shadow, size_t shadow_bytes, void *dX);
 int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, float *dH);
 int rz_tc_wait_selftest(long long limit_cycles, cudaStream_t stream);

@@ -9,18 +9,30 @@
 // a fixed array that is part of the library image.
 //
 // Consequences of the fixed array, all of which the caller has to know:
-//   * capacity: the shadow of the problem must fit RZ_NOALLOC_SCRATCH_BYTES (16 MiB), i.e.
-//     H <= 2^20 elements for both the bf16 and the tf32 paths; larger problems are refused with
-//     RZ_ERR_TOO_LARGE and nothing is launched;
+//   * capacity: the shifted copies of the hashed array must fit RZ_NOALLOC_SCRATCH_BYTES (16 MiB):
+//     8 copies x 2 bytes (bf16 path) or 4 copies x 4 bytes (tf32 / fp32 paths) per element, H rounded
+//     up to a multiple of 64, i.e. H <= 2^20.  Shapes for which the ordinary entry point would also put
+//     a split-contraction workspace into the scratch (small batches with long contractions) still run:
+//     when the workspace does not fit next to the copies the launch does every block's whole
+//     contraction instead (same result, fewer CTAs busy).  The one exception is fp32 precision with a
+//     contraction longer than 2048, where the split is what bounds the rounding error: there copies
+//     plus workspace must fit, else RZ_ERR_TOO_LARGE.  A refused call launches nothing;
 //   * every GPU on which the library's module gets loaded holds those 16 MiB until the process exits;
-//   * the first call on a device looks up the array's device address (once per device, with that
-//     device current).  Make that first call before any stream capture begins;
 //   * there is one array per device and every call rewrites it, so two calls whose kernels can overlap
 //     on the GPU (different streams, no ordering between them) race on it.  Calls on one stream, or
 //     ordered by events, are fine.  Nothing in the array has to start at zero: each call rewrites
-//     every byte the kernel will read, including the padding past the end of the hashed array.
+//     every byte the kernel will read, including the padding past the end of the hashed array, and
+//     zeroes the workspace part when it uses it.
 //
-// The call itself performs no cudaMalloc / cudaFree and uses no allocating library routine.
+// The call allocates no device memory: no cudaMalloc / cudaFree of a real pointer and no allocating library
+// routine.  What does happen once, and belongs before any stream capture: the first call on a device looks up
+// the array's device address (with that device current) and the library's status words, and pins one page of
+// the library's own host data for the status copy; the first call of a host thread binds the device's primary
+// context to it (a null cudaFree); the first launch of each kernel variant on a device sets that variant's
+// shared-memory attribute and queries its occupancy.  A new shape can select a variant not used before, so warm
+// up every shape that will be captured.
+#include <atomic>
+
 #include "rz_common.h"
 
 namespace {
@@ -31,7 +43,7 @@ constexpr int RZ_NOALLOC_MAX_DEVICES = 64;
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not a device pointer.
 static __device__ __align__(256) unsigned char g_rz_noalloc_scratch[RZ_NOALLOC_SCRATCH_BYTES];
 
-void *g_scratch_ptr[RZ_NOALLOC_MAX_DEVICES] = {nullptr};
+std::atomic<void *> g_scratch_ptr[RZ_NOALLOC_MAX_DEVICES];
 
 // Device address of the scratch array on the current device; resolved once per device.
 int scratch_address(void **out)
@@ -40,14 +52,14 @@ int scratch_address(void **out)
     int st = rz_record_cuda(cudaGetDevice(&dev), "cudaGetDevice");
     if (st) return st;
     if (dev < 0 || dev >= RZ_NOALLOC_MAX_DEVICES) return RZ_ERR_UNSUPPORTED;
-    if (!g_scratch_ptr[dev]) {
-        void *ptr = nullptr;
+    void *ptr = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!ptr) {
         st = rz_record_cuda(cudaGetSymbolAddress(&ptr, g_rz_noalloc_scratch), "cudaGetSymbolAddress(noalloc scratch)");
         if (st) return st;
         if (!ptr) return RZ_ERR_CUDA;
-        g_scratch_ptr[dev] = ptr;
+        g_scratch_ptr[dev].store(ptr, std::memory_order_release);   // (a second thread would store the same address)
     }
-    *out = g_scratch_ptr[dev];
+    *out = ptr;
     return RZ_OK;
 }
 
@@ -59,16 +71,17 @@ int rz_linear_forward_noalloc(const rz_problem *pb, const void *X, const float *
                               void *stream)
 {
     // Problems that take the FMA kernels need no scratch at all: same call as the ordinary entry point.
-    const size_t need = rz_shadow_bytes(pb);
-    if (need == 0) return rz_linear_forward(pb, X, hashed, nullptr, bias, Y, stream);
-    if (need > RZ_NOALLOC_SCRATCH_BYTES) return RZ_ERR_TOO_LARGE;
+    const size_t full = rz_shadow_bytes(pb);
+    if (full == 0) return rz_linear_forward(pb, X, hashed, nullptr, 0, bias, Y, stream);
+    if (rz_tc_copies_bytes(pb) > RZ_NOALLOC_SCRATCH_BYTES) return RZ_ERR_TOO_LARGE;
+    if (full > RZ_NOALLOC_SCRATCH_BYTES && rz_tc_needs_workspace(pb, RZ_OP_FORWARD)) return RZ_ERR_TOO_LARGE;
     if (!X || !hashed || !Y) return RZ_ERR_NULL;
     void *scratch = nullptr;
     int st = scratch_address(&scratch);
     if (st) return st;
     st = rz_shadow_refresh(pb, hashed, scratch, stream);
     if (st) return st;
-    return rz_linear_forward(pb, X, hashed, scratch, bias, Y, stream);
+    return rz_forward_with_scratch(pb, X, hashed, scratch, RZ_NOALLOC_SCRATCH_BYTES, bias, Y, stream, true);
 }
 
 }  // extern "C"

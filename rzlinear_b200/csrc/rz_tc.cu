@@ -90,7 +90,8 @@ struct TcParams {
     uint32_t nsplit, chunks_per_split;   // blocks from index n_main on are split into nsplit parts of the contraction
     uint32_t n_main;                      // blocks [0, n_main) run their whole contraction in one work item
     uint32_t total_items;
-    uint32_t br;                // OP_DX: slice rows per B box
+    uint32_t br;                // slice rows per B box (FWD: min(BK, stage depth); DX: min(BK, B columns of this CTA))
+    uint32_t kparts;            // FWD: B boxes along the contraction per 128-byte column block (stage depth / br)
     uint32_t group_rows;        // row tiles per rasterisation group
     uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;  // descriptor strides, bytes
     uint32_t a_layout, b_layout;                            // descriptor swizzle layout type
@@ -101,8 +102,7 @@ struct TcParams {
     void *out;
     float *dH;
     float *ws;                  // FWD / DX with a split contraction: fp32 partial sums [rows][cols]
-    int *status;
-    long long wait_limit;
+    WaitCtx wait;               // where bounded waits report, and this launch's epoch
     uint32_t tma_store;         // FWD / DX: write the output with bulk tensor stores (0 = plain 16-byte stores)
 };
 
@@ -249,12 +249,14 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             for (uint32_t cb = c_begin; cb < c_end && ok; cb += BATCH) {
                 const uint32_t nb = min((uint32_t)BATCH, c_end - cb);
                 if (OP != OP_DW) {
-                    const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS : (uint32_t)B_COLS / p.br;
+                    const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS * p.kparts : (uint32_t)B_COLS / p.br;
                     for (uint32_t e = lane; e < nb * tps; e += 32) {
                         const uint32_t ci = e / tps, j = e - ci * tps;
                         uint32_t pk, pn, x_in, y_in;
                         if (OP == OP_FWD) {
-                            const uint32_t k0 = (cb + ci) * KC, n = col0 + j * EPR;
+                            // box j = (128-byte column block ja, part hh of the stage's contraction rows)
+                            const uint32_t ja = j / p.kparts, hh = j - ja * p.kparts;
+                            const uint32_t k0 = (cb + ci) * KC + hh * p.br, n = col0 + ja * EPR;
                             pk = k0 / (uint32_t)p.hash.BK;
                             y_in = k0 - pk * (uint32_t)p.hash.BK;
                             pn = n / (uint32_t)p.hash.BN;
@@ -277,7 +279,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 if (lane == 0) {
                     for (uint32_t ci = 0; ci < nb; ++ci) {
                         const uint32_t g = it + ci, s = g % STAGES, ph = (g / STAGES) & 1;
-                        if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1, RZ_WAIT_SMEM_EMPTY, p.status, p.wait_limit, 2000)) {
+                        if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1, RZ_WAIT_SMEM_EMPTY, p.wait, 2000)) {
                             ok = false;
                             it += ci;
                             break;
@@ -298,8 +300,8 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                                 else
                                     tma_load_2d(sa, &mapA, full, (int32_t)d0, (int32_t)row0);
                             }
-                            const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS : (uint32_t)B_COLS / p.br;
-                            const uint32_t box_bytes = (OP == OP_FWD) ? (uint32_t)ATOM : p.br * 128u;
+                            const uint32_t tps = (OP == OP_FWD) ? (uint32_t)B_ATOMS * p.kparts : (uint32_t)B_COLS / p.br;
+                            const uint32_t box_bytes = p.br * 128u;   // (FWD: boxes of one column block are consecutive)
                             for (uint32_t j = 0; j < tps; ++j) {
                                 const int32_t x = (int32_t)tab_x[ci * MAX_TPS + j], y = (int32_t)tab_y[ci * MAX_TPS + j],
                                               z = (int32_t)tab_z[ci * MAX_TPS + j];
@@ -344,12 +346,12 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             decode(item, tr, tc, c_begin, c_end);
             const uint32_t buf = n_items % NBUF, tph = (n_items / NBUF) & 1;
             if (lane == 0) {
-                if (!mbar_wait_bounded(bar_tempty + 8 * buf, tph ^ 1, RZ_WAIT_TMEM_EMPTY, p.status, p.wait_limit, 2000)) ok = false;
+                if (!mbar_wait_bounded(bar_tempty + 8 * buf, tph ^ 1, RZ_WAIT_TMEM_EMPTY, p.wait, 2000)) ok = false;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * RB * TILE_C;
                 for (uint32_t c = c_begin; c < c_end && ok; ++c, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (!mbar_wait_bounded((SPLIT ? bar_split : bar_full) + 8 * s, ph, RZ_WAIT_SMEM_FULL, p.status, p.wait_limit)) {
+                    if (!mbar_wait_bounded((SPLIT ? bar_split : bar_full) + 8 * s, ph, RZ_WAIT_SMEM_FULL, p.wait)) {
                         ok = false;
                         break;
                     }
@@ -417,7 +419,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             const uint32_t buf = n_items % NBUF, tph = (n_items / NBUF) & 1;
             // one lane per warp polls (sleeping in the barrier unit between polls); the others wait for it
             bool mine = true;
-            if (lane == 0) mine = mbar_wait_bounded(bar_tfull + 8 * buf, tph, RZ_WAIT_TMEM_FULL, p.status, p.wait_limit, 20000);
+            if (lane == 0) mine = mbar_wait_bounded(bar_tfull + 8 * buf, tph, RZ_WAIT_TMEM_FULL, p.wait, 20000);
             ok = __shfl_sync(0xffffffffu, (int)mine, 0) != 0;
             if (!ok) break;
             tc_fence_after();
@@ -697,7 +699,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             decode(item, tr, tc, c_begin, c_end);
             for (uint32_t c = c_begin; c < c_end && ok; ++c, ++it) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                bool mine = mbar_wait_bounded(bar_full + 8 * s, ph, RZ_WAIT_SMEM_FULL, p.status, p.wait_limit, 1000);
+                bool mine = mbar_wait_bounded(bar_full + 8 * s, ph, RZ_WAIT_SMEM_FULL, p.wait, 1000);
                 ok = __all_sync(0xffffffffu, mine);
                 if (!ok) break;
                 uint4 *hi = reinterpret_cast<uint4 *>(smem_gen + s * STAGE_BYTES);
@@ -740,13 +742,13 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
 // ---- self-test of the bounded-wait machinery ---------------------------------------------------
 // One thread waits on an mbarrier that nothing will ever complete.  The wait must give up after
 // `limit` cycles, leave its code in the status word and let the kernel return normally.
-__global__ void rz_wait_selftest_kernel(int *status, long long limit)
+__global__ void rz_wait_selftest_kernel(WaitCtx w)
 {
     __shared__ __align__(8) uint64_t bar;
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bar), 1);
         fence_barrier_init();
-        (void)mbar_wait_bounded(smem_u32(&bar), 0, RZ_WAIT_SELFTEST, status, limit);
+        (void)mbar_wait_bounded(smem_u32(&bar), 0, RZ_WAIT_SELFTEST, w);
     }
 }
 
@@ -822,6 +824,128 @@ __global__ void rz_sgd_momentum_kernel(float *__restrict__ hashed, const float *
         vel[i] = v;
         hashed[i] -= lr * v;
     }
+}
+
+// The optimiser step and the shadow refresh in ONE pass over the hashed array:
+//   (velocity = momentum * velocity + dH;)   hashed -= lr * (velocity | dH);   copy s, element j = convert(hashed[j + s]).
+// A thread owns one aligned group of NS elements: it updates them in place and writes the NS 16-byte pieces of the
+// shifted copies that start in its group.  Those pieces reach NS - 1 elements into the NEXT group, whose new values
+// come from the neighbouring lane (shuffle) or warp (shared memory) of the same 256-group chunk.  The last group of
+// a chunk has its neighbour in another block, which may or may not have updated it yet: its pieces for copies
+// 1 .. NS-1 are left to the block that finishes last (a ticket counter tells which), which by then reads final values.
+constexpr int SGD_CHUNK = 256;     // groups per block iteration (= threads per block)
+constexpr int SGD_TICKETS = 64;    // launches that may be in flight at once, one ticket word each
+__device__ unsigned g_sgd_ticket[SGD_TICKETS];
+
+template <bool TF32>
+__device__ __forceinline__ uint4 shadow_piece(const float *v, int raw)
+{
+    uint4 u;
+    if (TF32) {
+        u.x = raw ? __float_as_uint(v[0]) : to_tf32(v[0]);
+        u.y = raw ? __float_as_uint(v[1]) : to_tf32(v[1]);
+        u.z = raw ? __float_as_uint(v[2]) : to_tf32(v[2]);
+        u.w = raw ? __float_as_uint(v[3]) : to_tf32(v[3]);
+    } else {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+        u.x = *reinterpret_cast<uint32_t *>(&h0);
+        u.y = *reinterpret_cast<uint32_t *>(&h1);
+        u.z = *reinterpret_cast<uint32_t *>(&h2);
+        u.w = *reinterpret_cast<uint32_t *>(&h3);
+    }
+    return u;
+}
+
+template <bool TF32, bool MOMENTUM>
+__global__ void __launch_bounds__(SGD_CHUNK)
+rz_sgd_shadow_kernel(float *__restrict__ hashed, const float *__restrict__ dH, float *__restrict__ vel, float lr, float momentum,
+                     uint8_t *__restrict__ shadow, uint32_t H, uint32_t Hc, size_t copy_stride, int raw, unsigned *ticket)
+{
+    constexpr int NS = TF32 ? 4 : 8;
+    __shared__ float first_of_warp[SGD_CHUNK / 32][NS];
+    __shared__ bool is_last;
+    const uint32_t groups = Hc / NS, nchunks = (groups + SGD_CHUNK - 1) / SGD_CHUNK;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t chunk = blockIdx.x; chunk < nchunks; chunk += gridDim.x) {
+        const uint32_t g = chunk * SGD_CHUNK + threadIdx.x, j0 = g * NS;
+        float nv[2 * NS];   // new values of this group, then of the next one
+#pragma unroll
+        for (int i = 0; i < NS; ++i) nv[i] = 0.f;
+        if (g < groups && j0 < H) {
+            if (j0 + NS <= H) {
+#pragma unroll
+                for (int q = 0; q < NS / 4; ++q) {
+                    float4 h = reinterpret_cast<float4 *>(hashed + j0)[q];
+                    float4 d = reinterpret_cast<const float4 *>(dH + j0)[q];
+                    if (MOMENTUM) {
+                        const float4 v = reinterpret_cast<float4 *>(vel + j0)[q];
+                        d.x = momentum * v.x + d.x, d.y = momentum * v.y + d.y, d.z = momentum * v.z + d.z, d.w = momentum * v.w + d.w;
+                        reinterpret_cast<float4 *>(vel + j0)[q] = d;
+                    }
+                    h.x -= lr * d.x, h.y -= lr * d.y, h.z -= lr * d.z, h.w -= lr * d.w;
+                    reinterpret_cast<float4 *>(hashed + j0)[q] = h;
+                    nv[4 * q + 0] = h.x, nv[4 * q + 1] = h.y, nv[4 * q + 2] = h.z, nv[4 * q + 3] = h.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+                    if (j0 + i < H) {
+                        float d = dH[j0 + i];
+                        if (MOMENTUM) {
+                            d = momentum * vel[j0 + i] + d;
+                            vel[j0 + i] = d;
+                        }
+                        nv[i] = hashed[j0 + i] - lr * d;
+                        hashed[j0 + i] = nv[i];
+                    }
+                }
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < NS; ++i) first_of_warp[warp][i] = nv[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < NS; ++i) nv[NS + i] = __shfl_down_sync(0xffffffffu, nv[i], 1);
+        const bool chunk_end = threadIdx.x == SGD_CHUNK - 1;
+        if (lane == 31 && !chunk_end) {
+#pragma unroll
+            for (int i = 0; i < NS; ++i) nv[NS + i] = first_of_warp[warp + 1][i];
+        }
+        const bool deferred = chunk_end && g + 1 < groups;   // the neighbour group belongs to another block
+        if (chunk_end) {
+#pragma unroll
+            for (int i = 0; i < NS; ++i) nv[NS + i] = 0.f;   // (past the end of the array when not deferred)
+        }
+        if (g < groups) {
+#pragma unroll
+            for (int s2 = 0; s2 < NS; ++s2)
+                if (s2 == 0 || !deferred)
+                    *reinterpret_cast<uint4 *>(shadow + s2 * copy_stride + (size_t)g * 16) = shadow_piece<TF32>(nv + s2, raw);
+        }
+        __syncthreads();   // first_of_warp is rewritten by the next chunk
+    }
+    // the block that finishes last fills in the pieces that straddle chunk boundaries
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (uint32_t b = threadIdx.x; b + 1 < nchunks; b += SGD_CHUNK) {
+        const uint32_t g = b * SGD_CHUNK + SGD_CHUNK - 1, j0 = g * NS;
+        float nv[2 * NS];
+#pragma unroll
+        for (int i = 0; i < 2 * NS; ++i) nv[i] = (j0 + i < H) ? __ldcg(hashed + j0 + i) : 0.f;
+#pragma unroll
+        for (int s2 = 1; s2 < NS; ++s2)
+            *reinterpret_cast<uint4 *>(shadow + s2 * copy_stride + (size_t)g * 16) = shadow_piece<TF32>(nv + s2, raw);
+    }
+    if (threadIdx.x == 0) *ticket = 0;   // ready for the next launch that draws this ticket word
 }
 
 // out = convert(alpha * partial_sums (+ bias) (ReLU)) for the blocks of a FWD / DX launch whose contraction was
@@ -906,9 +1030,36 @@ Geometry geometry(const rz_problem *pb)
 
 // `mn_major`: the tile feeds an M/N-major operand; for 32-bit elements that needs the 32-byte-chunk flavour
 // of the 128-byte swizzle, every other case uses the 16-byte-chunk one.
+// Encoded maps are pure functions of (base, type, swizzle flavour, extents, strides, box): each host thread keeps
+// the last few it made, so steady-state launches (the same tensors step after step) encode nothing.
+struct MapKey {
+    const void *base;
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    int rank, tf32, mn_major;
+    bool operator==(const MapKey &o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapCache {
+    static constexpr int N = 16;
+    MapKey key[N];
+    alignas(64) CUtensorMap map[N];
+    int used = 0, next = 0;
+};
+
 int encode(CUtensorMap *map, bool tf32, bool mn_major, void *base, int rank, const uint64_t *dims,
            const uint64_t *strides_bytes, const uint32_t *box)
 {
+    static thread_local MapCache cache;
+    MapKey k;
+    memset(&k, 0, sizeof(k));   // (padding too: keys are compared bytewise)
+    k.base = base, k.rank = rank, k.tf32 = tf32, k.mn_major = mn_major;
+    for (int i = 0; i < rank; ++i) k.dims[i] = dims[i], k.box[i] = box[i];
+    for (int i = 0; i + 1 < rank; ++i) k.strides[i] = strides_bytes[i];
+    for (int i = 0; i < cache.used; ++i)
+        if (cache.key[i] == k) {
+            *map = cache.map[i];
+            return RZ_OK;
+        }
     EncodeTiledFn fn = get_encode();
     if (!fn) return rz_record_cuda(cudaErrorUnknown, "cuTensorMapEncodeTiled not available");
     // The encoder is a driver call and wants a context current on this thread.  A thread that has made no
@@ -937,6 +1088,9 @@ int encode(CUtensorMap *map, bool tf32, bool mn_major, void *base, int rank, con
         snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed (CUresult %d, rank %d)", (int)r, rank);
         return rz_record_cuda(cudaErrorInvalidValue, msg);
     }
+    const int slot = cache.used < MapCache::N ? cache.used++ : (cache.next = (cache.next + 1) % MapCache::N);
+    cache.key[slot] = k;
+    cache.map[slot] = *map;
     return RZ_OK;
 }
 
@@ -953,10 +1107,45 @@ int num_sms()
     return cached[dev];
 }
 
+// SMs a launch may occupy: all of them, less the ones the problem asks to leave idle (a collective that should
+// run beside a persistent kernel needs SMs of its own); never fewer than two.
+int usable_sms(const rz_problem *pb)
+{
+    int n = num_sms() - (pb->sm_reserve > 0 ? pb->sm_reserve : 0);
+    return n < 2 ? 2 : n;
+}
+
 uint32_t env_u32(const char *name, uint32_t dflt)
 {
     const char *s = getenv(name);
     return s ? (uint32_t)strtoul(s, nullptr, 0) : dflt;
+}
+
+// Bring-up / A-B knobs, read from the environment once (rz_reload_env() reads them again):
+//   RZ_TC_CONFIG 1..5 forces a block shape, RZ_TC_NOSPLIT=1 turns contraction splitting off, RZ_TC_EW_STAGES is the
+//   longest contraction (stages) that gets the sixteen-warp weight-gradient epilogue, RZ_TC_GROUP the rasterisation
+//   group (row tiles), RZ_TC_TMA_STORE=0 plain stores instead of bulk tensor stores, RZ_TC_VERBOSE=1 one line per launch.
+struct Knobs {
+    std::atomic<uint32_t> config{0}, no_split{0}, ew_stages{64}, group{0}, tma_store{1}, verbose{0};
+    std::atomic<bool> ready{false};
+};
+Knobs g_knobs;
+
+void load_knobs()
+{
+    g_knobs.config.store(env_u32("RZ_TC_CONFIG", 0));
+    g_knobs.no_split.store(env_u32("RZ_TC_NOSPLIT", 0));
+    g_knobs.ew_stages.store(env_u32("RZ_TC_EW_STAGES", 64));
+    g_knobs.group.store(env_u32("RZ_TC_GROUP", 0));
+    g_knobs.tma_store.store(env_u32("RZ_TC_TMA_STORE", 1));
+    g_knobs.verbose.store(env_u32("RZ_TC_VERBOSE", 0));
+    g_knobs.ready.store(true, std::memory_order_release);
+}
+
+const Knobs &knobs()
+{
+    if (!g_knobs.ready.load(std::memory_order_acquire)) load_knobs();
+    return g_knobs;
 }
 
 // Block shape of a launch.  (ctas, rb, nc): CTAs per block (2 = cluster pair driving cta_group::2 MMAs), row
@@ -989,7 +1178,7 @@ TcConfig choose_config(const rz_problem *pb, int op)
     const int64_t cols = (op == RZ_OP_BACKWARD_INPUT) ? pb->K : pb->N;
     const int64_t depth = (op == RZ_OP_FORWARD) ? pb->K : (op == RZ_OP_BACKWARD_INPUT ? pb->N : pb->M);
     const int64_t stages = (depth + (bf16 ? 63 : 31)) / (bf16 ? 64 : 32);
-    const int sms = num_sms();
+    const int sms = usable_sms(pb);
     auto allowed = [&](const TcConfig &c) {
         if (split && c.rb == 2) return false;                       // split precision has no two-row-block variant
         // with two row blocks the epilogue cannot overlap the next main loop: the contraction must amortise it
@@ -1010,8 +1199,8 @@ TcConfig choose_config(const rz_problem *pb, int op)
         if (most < 1) most = 1;
         return want < most ? want : most;
     };
-    const uint32_t forced = env_u32("RZ_TC_CONFIG", 0);
-    const bool no_split = env_u32("RZ_TC_NOSPLIT", 0) != 0;
+    const uint32_t forced = knobs().config.load(std::memory_order_relaxed);
+    const bool no_split = knobs().no_split.load(std::memory_order_relaxed) != 0;
     TcConfig best = kCandidates[4].cfg;
     double best_score = -1.0;
     for (int i = 0; i < 5; ++i) {
@@ -1053,7 +1242,7 @@ TcConfig choose_config(const rz_problem *pb, int op)
         }
         // Weight gradient of a short contraction: the scatter epilogue (one reduction per 32 elements, issued by
         // one warp per scheduler) outlasts the main loop; sixteen epilogue warps hide its instruction latency.
-        if (op == RZ_OP_BACKWARD_WEIGHT && !split && c.rb == 1 && stages / c.nsplit <= (int64_t)env_u32("RZ_TC_EW_STAGES", 64))
+        if (op == RZ_OP_BACKWARD_WEIGHT && !split && c.rb == 1 && stages / c.nsplit <= (int64_t)knobs().ew_stages.load(std::memory_order_relaxed))
             c.ew = 4;
         if (forced >= 1 && forced <= 5) {
             static const int order[5] = {2, 1, 0, 3, 4};
@@ -1101,6 +1290,13 @@ uint32_t dx_box_rows(const rz_problem *pb, const TcConfig &c)
     return (uint32_t)pb->BK < bcols ? (uint32_t)pb->BK : bcols;
 }
 
+// FWD: slice rows per B box - a stage's contraction rows, or one hash tile of them when tiles are shorter
+uint32_t fwd_box_rows(const rz_problem *pb)
+{
+    const uint32_t kc = pb->precision == RZ_PREC_BF16 ? 64u : 32u;
+    return (uint32_t)pb->BK < kc ? (uint32_t)pb->BK : kc;
+}
+
 template <int OP, bool TF32, int CTAS, int RB, int SPLIT, int NC, int EW = 1>
 int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &mapB, const CUtensorMap &mapC, TcParams &p,
               const TcConfig &plan)
@@ -1123,9 +1319,10 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.tiles_r = (p.rows + ITEM_R - 1) / ITEM_R;
     p.tiles_c = (p.cols + NC - 1) / NC;
     p.nchunks = (depth + KC - 1) / KC;
-    p.br = dx_box_rows(pb, TcConfig{CTAS, RB, NC});
-    p.group_rows = env_u32("RZ_TC_GROUP", GROUP_ROWS / RB);
-    if (p.group_rows < 1) p.group_rows = 1;
+    p.br = OP == OP_FWD ? fwd_box_rows(pb) : dx_box_rows(pb, TcConfig{CTAS, RB, NC});
+    p.kparts = KC / fwd_box_rows(pb);
+    p.group_rows = knobs().group.load(std::memory_order_relaxed);
+    if (p.group_rows < 1) p.group_rows = GROUP_ROWS / RB;
 
     auto kern = rz_tc_kernel<OP, TF32, CTAS, RB, SPLIT, NC, EW>;
     constexpr int SMEM_TOTAL = smem_total(OP, CTAS, RB, SPLIT, NC, EW);
@@ -1172,6 +1369,10 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
         }
     }
     if (!known && cacheable) ready[dev].store(slots + 1, std::memory_order_release);
+    if (pb->sm_reserve > 0) {   // leave SMs idle for whatever the caller runs beside this kernel
+        slots -= (pb->sm_reserve + CTAS - 1) / CTAS;
+        if (slots < 1) slots = 1;
+    }
 
     const uint32_t tiles = p.tiles_r * p.tiles_c;
     p.nsplit = plan.nsplit > 1 ? (uint32_t)plan.nsplit : 1u;
@@ -1185,10 +1386,9 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.total_items = p.n_main + (tiles - p.n_main) * p.nsplit;
     p.alpha = pb->alpha;
     p.relu = (pb->flags & RZ_FLAG_RELU) ? 1 : 0;
-    p.status = rz_device_status_word();
-    if (!p.status) return rz_record_cuda(cudaErrorUnknown, "status word address");
-    p.wait_limit = 2000000000ll;
-    p.tma_store = env_u32("RZ_TC_TMA_STORE", 1);
+    st = rz_wait_context(&p.wait, 2000000000ll);   // also refuses to launch behind a kernel whose wait gave up
+    if (st) return st;
+    p.tma_store = knobs().tma_store.load(std::memory_order_relaxed);
 
     // shared-memory descriptors (bytes)
     const uint32_t atom = KC * 128;
@@ -1213,8 +1413,7 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (a_major << 15) | (b_major << 16) | ((uint32_t)(NC >> 3) << 17) |
               ((uint32_t)(PAIR_R >> 4) << 24);
 
-    static const bool verbose = env_u32("RZ_TC_VERBOSE", 0) != 0;   // bring-up aid: one line per launch on stderr
-    if (verbose)
+    if (knobs().verbose.load(std::memory_order_relaxed))   // bring-up aid: one line per launch on stderr
         fprintf(stderr, "rz_tc op %d tf32 %d block (%d,%d,%d) ew %d stages %d: %u blocks, %u whole + %u x %u parts, %d slots\n", OP,
                 (int)TF32, CTAS, RB, NC, EW, STAGES_HOST, tiles, p.n_main, tiles - p.n_main, p.nsplit, slots);
     const uint32_t blocks = p.total_items < (uint32_t)slots ? p.total_items : (uint32_t)slots;
@@ -1307,9 +1506,10 @@ int map_shadow(CUtensorMap *map, const rz_problem *pb, bool mn_major, const void
 
 int rz_tc_wait_selftest(long long limit_cycles, cudaStream_t stream)
 {
-    int *status = rz_device_status_word();
-    if (!status) return rz_record_cuda(cudaErrorUnknown, "status word address");
-    rz_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, limit_cycles);
+    RzWaitCtx w;
+    int st = rz_wait_context(&w, limit_cycles);
+    if (st) return st;
+    rz_wait_selftest_kernel<<<1, 32, 0, stream>>>(w);
     rz_count_launch(1);
     return rz_record_cuda(cudaGetLastError(), "wait self-test launch");
 }
@@ -1318,26 +1518,52 @@ bool rz_tc_supported(const rz_problem *pb, int op)
 {
     (void)op;
     const Geometry g = geometry(pb);
-    if (pb->BK % g.epr || pb->BN % g.epr) return false;
+    // a 128-byte operand row must lie inside one hash tile along n; along k a pipeline stage (one such row of
+    // contraction elements) is made of whole hash tiles or lies inside one, and tiles are multiples of the 32 rows
+    // an epilogue warp scatters
+    if (pb->BN % g.epr || pb->BK % 32) return false;
+    if (pb->BK < g.epr ? (g.epr % pb->BK != 0) : (pb->BK % g.epr != 0)) return false;
     if (pb->BK <= 64 ? (64 % pb->BK != 0) : (pb->BK % 64 != 0)) return false;   // whole B boxes per hash tile (narrowest block)
     if ((pb->K * g.es) % 16 || (pb->N * g.es) % 16) return false;
     if (pb->K < g.epr || pb->N < g.epr) return false;   // at least one full 128-byte row of every operand
     return true;
 }
 
+size_t rz_tc_copies_bytes(const rz_problem *pb)
+{
+    const Geometry g = geometry(pb);
+    return g.copy_stride * (size_t)g.ns;
+}
+
 size_t rz_tc_shadow_bytes(const rz_problem *pb)
 {
     // the shifted copies, then the fp32 workspace of split-contraction launches (forward and input gradient share it)
-    const Geometry g = geometry(pb);
     const size_t wf = workspace_bytes(pb, RZ_OP_FORWARD), wi = workspace_bytes(pb, RZ_OP_BACKWARD_INPUT);
-    return g.copy_stride * (size_t)g.ns + (wf > wi ? wf : wi);
+    return rz_tc_copies_bytes(pb) + (wf > wi ? wf : wi);
 }
 
-static float *workspace_of(const rz_problem *pb, const void *shadow, int op)
+bool rz_tc_needs_workspace(const rz_problem *pb, int op)
 {
-    if (workspace_bytes(pb, op) == 0) return nullptr;
-    const Geometry g = geometry(pb);
-    return reinterpret_cast<float *>(const_cast<uint8_t *>(static_cast<const uint8_t *>(shadow)) + g.copy_stride * (size_t)g.ns);
+    // split precision bounds its accumulation chains by splitting long contractions: that launch cannot do without
+    if (pb->precision != RZ_PREC_FP32 || op == RZ_OP_BACKWARD_WEIGHT) return false;
+    return (op == RZ_OP_FORWARD ? pb->K : pb->N) > 2048;
+}
+
+void rz_tc_reload_env() { load_knobs(); }
+
+// Workspace of a launch inside the caller's scratch: behind the copies, if the scratch is large enough to hold it
+// (a scratch that only holds the copies makes the launch run every block's whole contraction instead).
+static int workspace_of(const rz_problem *pb, void *shadow, size_t shadow_bytes, int op, float **ws)
+{
+    *ws = nullptr;
+    const size_t need = workspace_bytes(pb, op), copies = rz_tc_copies_bytes(pb);
+    if (shadow_bytes < copies) return RZ_ERR_SCRATCH;
+    if (need == 0) return RZ_OK;
+    if (shadow_bytes >= copies + need)
+        *ws = reinterpret_cast<float *>(static_cast<uint8_t *>(shadow) + copies);
+    else if (rz_tc_needs_workspace(pb, op))
+        return RZ_ERR_SCRATCH;
+    return RZ_OK;
 }
 
 int rz_tc_shadow_refresh(const RzLaunchCtx &c, const float *hashed, void *shadow)
@@ -1355,47 +1581,60 @@ int rz_tc_shadow_refresh(const RzLaunchCtx &c, const float *hashed, void *shadow
     return rz_record_cuda(cudaGetLastError(), "shadow refresh launch");
 }
 
-int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float lr, void *shadow)
+int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float *velocity, float lr, float momentum, void *shadow)
 {
     const uint32_t H = (uint32_t)c.pb->H;
-    uint32_t blocks = (H / 4 + 255) / 256;
-    if (blocks < 1) blocks = 1;
+    if (!shadow) {   // no tensor-core scratch to keep in step: the update alone
+        uint32_t blocks = velocity ? (H + 255) / 256 : (H / 4 + 255) / 256;
+        if (blocks < 1) blocks = 1;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (velocity) rz_sgd_momentum_kernel<<<blocks, 256, 0, c.stream>>>(hashed, dH, velocity, lr, momentum, H);
+        else rz_sgd_kernel<<<blocks, 256, 0, c.stream>>>(hashed, dH, lr, H);
+        rz_count_launch(1);
+        return rz_record_cuda(cudaGetLastError(), "sgd launch");
+    }
+    // update + shadow refresh in one pass; each launch in flight draws its own ticket word
+    static std::atomic<unsigned> next_ticket{0};
+    const unsigned slot = next_ticket.fetch_add(1, std::memory_order_relaxed) % SGD_TICKETS;
+    unsigned *ticket = nullptr;
+    int st = rz_record_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(&ticket), g_sgd_ticket), "ticket address");
+    if (st) return st;
+    ticket += slot;
+    const Geometry g = geometry(c.pb);
+    const uint32_t groups = g.Hc / g.ns;
+    uint32_t blocks = (groups + SGD_CHUNK - 1) / SGD_CHUNK;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    rz_sgd_kernel<<<blocks, 256, 0, c.stream>>>(hashed, dH, lr, H);
+    const bool tf32 = c.pb->precision != RZ_PREC_BF16;
+    const int raw = c.pb->precision == RZ_PREC_FP32 ? 1 : 0;
+    uint8_t *sh = static_cast<uint8_t *>(shadow);
+    if (tf32 && velocity)
+        rz_sgd_shadow_kernel<true, true><<<blocks, SGD_CHUNK, 0, c.stream>>>(hashed, dH, velocity, lr, momentum, sh, H, g.Hc, g.copy_stride, raw, ticket);
+    else if (tf32)
+        rz_sgd_shadow_kernel<true, false><<<blocks, SGD_CHUNK, 0, c.stream>>>(hashed, dH, nullptr, lr, 0.f, sh, H, g.Hc, g.copy_stride, raw, ticket);
+    else if (velocity)
+        rz_sgd_shadow_kernel<false, true><<<blocks, SGD_CHUNK, 0, c.stream>>>(hashed, dH, velocity, lr, momentum, sh, H, g.Hc, g.copy_stride, 0, ticket);
+    else
+        rz_sgd_shadow_kernel<false, false><<<blocks, SGD_CHUNK, 0, c.stream>>>(hashed, dH, nullptr, lr, 0.f, sh, H, g.Hc, g.copy_stride, 0, ticket);
     rz_count_launch(1);
-    int st = rz_record_cuda(cudaGetLastError(), "sgd launch");
-    if (st || !shadow) return st;
-    return rz_tc_shadow_refresh(c, hashed, shadow);
+    return rz_record_cuda(cudaGetLastError(), "sgd + shadow launch");
 }
 
-int rz_tc_sgd_momentum_step(const RzLaunchCtx &c, float *hashed, const float *dH, float *velocity, float lr, float momentum,
-                            void *shadow)
-{
-    const uint32_t H = (uint32_t)c.pb->H;
-    uint32_t blocks = (H + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    rz_sgd_momentum_kernel<<<blocks, 256, 0, c.stream>>>(hashed, dH, velocity, lr, momentum, H);
-    rz_count_launch(1);
-    int st = rz_record_cuda(cudaGetLastError(), "sgd momentum launch");
-    if (st || !shadow) return st;
-    return rz_tc_shadow_refresh(c, hashed, shadow);
-}
-
-int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const float *bias, void *Y)
+int rz_tc_forward(const RzLaunchCtx &c, const void *X, void *shadow, size_t shadow_bytes, const float *bias, void *Y)
 {
     const rz_problem *pb = c.pb;
     const bool tf32 = pb->precision != RZ_PREC_BF16;
     const Geometry g = geometry(pb);
-    CUtensorMap mapA, mapB;
-    int st = map_matrix(&mapA, tf32, false, X, pb->M, pb->K, g.epr, TILE_R);
-    if (st) return st;
-    st = map_shadow(&mapB, pb, true, shadow, g.epr);
-    if (st) return st;
     TcParams p;
     memset(&p, 0, sizeof(p));
     p.bias = bias;
     p.out = Y;
-    p.ws = workspace_of(pb, shadow, RZ_OP_FORWARD);
+    int st = workspace_of(pb, shadow, shadow_bytes, RZ_OP_FORWARD, &p.ws);
+    if (st) return st;
+    CUtensorMap mapA, mapB;
+    st = map_matrix(&mapA, tf32, false, X, pb->M, pb->K, g.epr, TILE_R);
+    if (st) return st;
+    st = map_shadow(&mapB, pb, true, shadow, fwd_box_rows(pb));
+    if (st) return st;
     // output map for the epilogue's bulk stores: 32-row x 128-byte boxes
     CUtensorMap mapC;
     st = map_matrix(&mapC, tf32, false, Y, pb->M, pb->N, g.epr, 32);
@@ -1403,21 +1642,22 @@ int rz_tc_forward(const RzLaunchCtx &c, const void *X, const void *shadow, const
     return launch_tc_any<OP_FWD>(c, mapA, mapB, mapC, p, choose_config(pb, RZ_OP_FORWARD));
 }
 
-int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, const void *shadow, void *dX)
+int rz_tc_backward_input(const RzLaunchCtx &c, const void *dY, void *shadow, size_t shadow_bytes, void *dX)
 {
     const rz_problem *pb = c.pb;
     const bool tf32 = pb->precision != RZ_PREC_BF16;
     const Geometry g = geometry(pb);
+    TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.out = dX;
+    int st = workspace_of(pb, shadow, shadow_bytes, RZ_OP_BACKWARD_INPUT, &p.ws);
+    if (st) return st;
     CUtensorMap mapA, mapB;
-    int st = map_matrix(&mapA, tf32, false, dY, pb->M, pb->N, g.epr, TILE_R);
+    st = map_matrix(&mapA, tf32, false, dY, pb->M, pb->N, g.epr, TILE_R);
     if (st) return st;
     const TcConfig config = choose_config(pb, RZ_OP_BACKWARD_INPUT);
     st = map_shadow(&mapB, pb, false, shadow, dx_box_rows(pb, config));
     if (st) return st;
-    TcParams p;
-    memset(&p, 0, sizeof(p));
-    p.out = dX;
-    p.ws = workspace_of(pb, shadow, RZ_OP_BACKWARD_INPUT);
     CUtensorMap mapC;
     st = map_matrix(&mapC, tf32, false, dX, pb->M, pb->K, g.epr, 32);
     if (st) return st;

@@ -4,7 +4,9 @@ Each rank owns M_local rows of X and dY; the hashed array and the random numbers
 Forward and input gradient need no communication.  The only exchange is the sum of the
 hashed-weight gradient over ranks (one all-reduce of H floats), launched right after the
 weight-gradient kernel so that it overlaps the input-gradient kernel; every rank then applies the
-same SGD update, so the replicas stay identical.
+same SGD update, so the replicas stay identical.  The input-gradient kernel is persistent (one CTA
+per SM), so with more than one rank it is launched on all SMs but `comm_sms`: the collective's
+CTAs get those and run beside it instead of behind it.
 
 The reference has no distributed code; this follows its single-GPU step
 (python/rz_linear/RzLinearFunction.py:14-60) per rank.
@@ -20,13 +22,26 @@ from . import _lib
 
 
 class CudaKernels:
-    """The C-ABI kernels (the only shipped implementation)."""
+    """The C-ABI kernels (the only shipped implementation).
 
-    def __init__(self, pb, device):
+    `comm_sms` > 0: the input-gradient kernel leaves that many SMs idle (for the all-reduce that runs
+    beside it).  The scratch is sized for the largest of the problems this object launches."""
+
+    def __init__(self, pb, device, comm_sms: int = 0):
         self.pb = pb
+        self.pb_dx = _lib.with_fields(pb, sm_reserve=int(comm_sms)) if comm_sms > 0 else pb
         self.device = device
-        nbytes = _lib.shadow_bytes(pb)
-        self.shadow = torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
+        self.shadow = None
+        self.reserve(max(_lib.shadow_bytes(pb), _lib.shadow_bytes(self.pb_dx)))
+
+    def reserve(self, nbytes: int, hashed=None) -> None:
+        """Grow the scratch to at least `nbytes` (never shrinks); refills it from `hashed` when it was replaced."""
+        have = 0 if self.shadow is None else self.shadow.numel()
+        if nbytes <= have:
+            return
+        self.shadow = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        if hashed is not None:
+            self.refresh(hashed)
 
     def refresh(self, hashed):
         if self.shadow is not None:
@@ -36,7 +51,7 @@ class CudaKernels:
         _lib.forward(self.pb, x, hashed, self.shadow, None, y)
 
     def backward_input(self, dy, hashed, dx):
-        _lib.backward_input(self.pb, dy, hashed, self.shadow, dx)
+        _lib.backward_input(self.pb_dx, dy, hashed, self.shadow, dx)
 
     def backward_weight(self, x, dy, dh):
         _lib.backward_weight(self.pb, x, dy, dh)
@@ -59,7 +74,8 @@ class RzDataParallelStep:
     def __init__(self, M_local: int, K: int, N: int, H: int, BK: int, BN: int, R: Sequence[int],
                  hash_mode: int = _lib.HASH_SINGLE, dtype: torch.dtype = torch.bfloat16, lr: float = 1e-3,
                  device="cuda", init_factor: float = 1.0, allow_tf32: bool = True,
-                 process_group: Optional[dist.ProcessGroup] = None, kernels=None, momentum: float = 0.0):
+                 process_group: Optional[dist.ProcessGroup] = None, kernels=None, momentum: float = 0.0,
+                 comm_sms: int = 8):
         self.M, self.K, self.N, self.H = M_local, K, N, H
         self.device = torch.device(device)
         self.dtype = dtype
@@ -70,7 +86,8 @@ class RzDataParallelStep:
         prec = _lib.PREC_BF16 if dtype == torch.bfloat16 else (_lib.PREC_TF32 if allow_tf32 else _lib.PREC_FP32)
         self.pb = _lib.make_problem(M_local, K, N, H, BK, BN, R, hash_mode, _lib.torch_io_dtype(dtype), prec,
                                     init_factor)
-        self.kernels = kernels if kernels is not None else CudaKernels(self.pb, self.device)
+        self.comm_sms = int(comm_sms) if self.world > 1 else 0
+        self.kernels = kernels if kernels is not None else CudaKernels(self.pb, self.device, self.comm_sms)
         self.hashed = torch.zeros(H, dtype=torch.float32, device=self.device)
         self.dH = torch.empty(H, dtype=torch.float32, device=self.device)
         self.velocity = torch.zeros(H, dtype=torch.float32, device=self.device) if self.momentum != 0.0 else None
@@ -106,6 +123,7 @@ class RzDataParallelStep:
         mark("backward_input")
         if work is not None:
             work.wait()
+        mark("comm_wait")   # what of the all-reduce was still running when the input gradient had finished
         self._update()
         mark("sgd")
 
@@ -118,9 +136,13 @@ class RzDataParallelStep:
         problems = []
         for i, (lo, hi) in enumerate(spans):
             flags = base.flags | (_lib.FLAG_ACCUMULATE_DH if i > 0 else 0)
-            pb = _lib.make_problem(hi - lo, self.K, self.N, self.H, base.BK, base.BN, list(base.R), base.hash_mode,
-                                   base.io_dtype, base.precision, base.alpha, flags)
-            problems.append(pb)
+            # the all-reduce is issued before the last chunk's input gradient and runs beside it
+            reserve = self.comm_sms if i == len(spans) - 1 else 0
+            problems.append((_lib.with_fields(base, M=hi - lo, flags=flags),
+                             _lib.with_fields(base, M=hi - lo, flags=flags, sm_reserve=reserve)))
+        # the split-contraction workspace inside the scratch depends on the rows of a launch: a remainder chunk
+        # can need more of it than the whole shard does
+        self.kernels.reserve(max(_lib.shadow_bytes(pb) for pair in problems for pb in pair), self.hashed)
         self._pipe = {
             "chunk_rows": chunk_rows, "spans": spans, "problems": problems,
             "x": torch.empty((self.M, self.K), dtype=self.dtype, device=self.device),
@@ -141,7 +163,7 @@ class RzDataParallelStep:
         `hashed_out_host` at the end."""
         if not isinstance(self.kernels, CudaKernels):
             raise RuntimeError("step_host drives the CUDA kernels; use step() with injected kernels")
-        pipe = self._host_pipeline(min(chunk_rows, self.M))
+        pipe = self._host_pipeline(min(chunk_rows, self.M))   # (may replace the scratch by a larger one)
         main = torch.cuda.current_stream(self.device)
         side = pipe["stream"]
         shadow = self.kernels.shadow
@@ -156,14 +178,14 @@ class RzDataParallelStep:
         work = None
         last = len(pipe["spans"]) - 1
         for i, (lo, hi) in enumerate(pipe["spans"]):
-            pb = pipe["problems"][i]
+            pb, pb_dx = pipe["problems"][i]
             x, dy = pipe["x"][lo:hi], pipe["dy"][lo:hi]
             main.wait_event(pipe["loaded"][i])
             _lib.forward(pb, x, self.hashed, shadow, None, self.Y[lo:hi])
             _lib.backward_weight(pb, x, dy, self.dH)
             if i == last and self.world > 1:
                 work = dist.all_reduce(self.dH, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-            _lib.backward_input(pb, dy, self.hashed, shadow, self.dX[lo:hi])
+            _lib.backward_input(pb_dx, dy, self.hashed, shadow, self.dX[lo:hi])
             ev = torch.cuda.Event()
             ev.record(main)
             pipe["consumed"][i] = ev

@@ -62,6 +62,55 @@ def alloc_shadow(pb, hashed: torch.Tensor) -> Optional[torch.Tensor]:
     return shadow
 
 
+_CACHE_ATTR = "_rz_shadow_cache"
+
+
+def cached_shadow(pb, hashed_weight: torch.Tensor, hashed_f32: torch.Tensor) -> Optional[torch.Tensor]:
+    """The shadow of `hashed_weight` for this problem, rebuilt only when the weights have changed.
+
+    The cache lives on the tensor object itself (so it dies with it and can never be mistaken for another
+    tensor that later reuses the address) as {(H, BK, BN, precision): entry}; an entry is valid while the
+    tensor's autograd version counter and data pointer are the ones it was filled at.  In-place updates
+    (optimisers, copy_, add_) bump the counter; writes through `.data` or from foreign code do not, exactly
+    as for autograd's own saved-tensor check: call `drop_shadow_cache(hashed_weight)` after such a write.
+    A forward on unchanged weights (evaluation, several layers sharing one hashed array, several
+    micro-batches per optimiser step) therefore allocates nothing and launches no refresh."""
+    _lib._require_cuda(hashed_f32)
+    nbytes = _lib.shadow_bytes(pb)
+    if nbytes == 0:
+        return None
+    cache = getattr(hashed_weight, _CACHE_ATTR, None)
+    if cache is None:
+        cache = {}
+        try:
+            setattr(hashed_weight, _CACHE_ATTR, cache)
+        except AttributeError:      # a tensor subclass without a __dict__: no caching
+            return alloc_shadow(pb, hashed_f32)
+    key = (pb.H, pb.BK, pb.BN, pb.precision)
+    version, ptr = hashed_weight._version, hashed_weight.data_ptr()
+    stream = torch.cuda.current_stream(hashed_f32.device)
+    entry = cache.get(key)
+    if entry is not None and entry["shadow"].numel() >= nbytes and entry["shadow"].device == hashed_f32.device:
+        if entry["version"] == version and entry["ptr"] == ptr:
+            if entry["stream"] != stream.cuda_stream:
+                stream.wait_event(entry["filled"])    # the refresh ran on another stream
+            return entry["shadow"]
+        shadow = entry["shadow"]                      # same buffer, new contents
+    else:
+        shadow = torch.empty(nbytes, dtype=torch.uint8, device=hashed_f32.device)
+    _lib.shadow_refresh(pb, hashed_f32, shadow)
+    filled = torch.cuda.Event()
+    filled.record(stream)
+    cache[key] = {"version": version, "ptr": ptr, "shadow": shadow, "stream": stream.cuda_stream, "filled": filled}
+    return shadow
+
+
+def drop_shadow_cache(hashed_weight: torch.Tensor) -> None:
+    """Forget the cached shadows of `hashed_weight` (after a write that autograd's version counter does not see)."""
+    if getattr(hashed_weight, _CACHE_ATTR, None):
+        getattr(hashed_weight, _CACHE_ATTR).clear()
+
+
 def rz_linear_forward_tl(input: torch.Tensor, hashed_weight: torch.Tensor, init_factor: float,
                          M: int, K: int, N: int, H: int,
                          R7: int, R6: int, R5: int, R4: int,

@@ -82,6 +82,35 @@ def test_step_from_host_buffers(rzlib):
     assert o.rel_l2(out.numpy(), _expected()[3]) < 1e-5
 
 
+def test_step_from_host_buffers_with_a_remainder_chunk(rzlib):
+    # Rows not a multiple of the chunk, contraction long enough (64 pipeline stages) that the small remainder chunk
+    # splits its contraction and so needs a larger workspace inside the scratch than the whole shard does: the step
+    # must size the scratch for its largest launch (a scratch that is too small is refused by the library).
+    from rzlinear_b200.dist import RzDataParallelStep
+    Mr, Kr, Nr, Hr, chunk = 8784, 4096, 4096, 1 << 17, 4096
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(Mr, Kr, generator=g).bfloat16()
+    dY = torch.randn(Mr, Nr, generator=g).bfloat16()
+    h = (torch.rand(Hr, generator=g) * 2 - 1) / Kr ** 0.5
+    step = RzDataParallelStep(Mr, Kr, Nr, Hr, 64, 64, R, rzlib.HASH_SINGLE, torch.bfloat16, LR, "cuda:0")
+    step.load_weights(h.cuda())
+    whole = rzlib.shadow_bytes(step.pb)
+    tail = rzlib.shadow_bytes(rzlib.with_fields(step.pb, M=Mr - chunk))
+    assert tail > whole                                         # the case this test is about
+    out = torch.empty(Hr, dtype=torch.float32).pin_memory()
+    step.step_host(X.pin_memory(), dY.pin_memory(), out, chunk_rows=chunk)
+    torch.cuda.synchronize()
+    assert rzlib.device_status() == (0, 0)
+    assert step.kernels.shadow.numel() >= tail
+    hb = o.bf16_round(h.numpy())
+    Xf, dYf = X.float().numpy(), dY.float().numpy()
+    dH = o.backward_weight(Xf, dYf, Hr, 64, 64, R, 0)
+    assert o.rel_l2(step.Y.float().cpu().numpy(), o.forward(Xf, hb, Nr, 64, 64, R, 0)) < 2e-3
+    assert o.rel_l2(step.dX.float().cpu().numpy(), o.backward_input(dYf, hb, Kr, 64, 64, R, 0)) < 2e-3
+    assert o.rel_l2(step.dH.cpu().numpy(), dH) < 2e-3
+    assert o.rel_l2(out.numpy(), h.numpy().astype(np.float64) - LR * dH) < 1e-5
+
+
 def _worker(rank, world, port, out_dir):
     import torch.distributed as dist
     from rzlinear_b200 import _lib

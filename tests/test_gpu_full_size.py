@@ -1,13 +1,19 @@
-"""Parity at the full sizes of the baseline configurations, where the CPU oracle is too slow.
+"""Parity at the full sizes of the baseline configurations, where a full CPU oracle pass is too slow.
 
-The tensor-core kernels are compared with the fp32 FMA kernels of the same library on the same inputs
-(those are pinned to the oracle and to the reference's fixtures at small sizes), and with properties that do
-not depend on size: the sum of the hashed-weight gradient equals alpha * sum_m (sum_k X[m,k]) (sum_n dY[m,n])
-because every element of X^T.dY is added exactly once, and the gradient is additive over row blocks.
+Three witnesses.  (1) The oracle on a sample: forward on sampled rows x sampled column tiles and input gradient
+on sampled rows x sampled row tiles of the virtual weight (oracle index arithmetic, fp64 products of exactly the
+operands the kernels see), and the hashed-weight gradient on sampled words - for word j the oracle enumerates
+every (k, n) whose element lands on j and the test sums X[:, k] . dY[:, n] in fp64.  (2) The fp32 FMA kernels of
+the same library on the same inputs (themselves pinned to the oracle and to the reference's fixtures at small
+sizes).  (3) Properties that do not depend on size: the sum of the hashed-weight gradient equals
+alpha * sum_m (sum_k X[m,k]) (sum_n dY[m,n]) because every element of X^T.dY is added exactly once, and the
+gradient is additive over row blocks.
 """
 import numpy as np
 import pytest
 import torch
+
+from oracle import rz_oracle as o
 
 pytestmark = pytest.mark.gpu
 
@@ -54,10 +60,45 @@ def case(rzlib, M, K, N, H, BK, BN, dtype, seed, h_scale, alpha=1.0):
     return pb, pb_ref, X, dY, h
 
 
+def check_against_oracle_sample(pb, X, dY, h, got, rows=256, words=320):
+    """The oracle's index arithmetic and fp64 products on a sample of the outputs (tolerance TOL_TC, rel-L2)."""
+    M, K, N, H, BK, BN = pb.M, pb.K, pb.N, pb.H, pb.BK, pb.BN
+    R, mode, alpha = list(pb.R), pb.hash_mode, float(pb.alpha)
+    rs = np.random.RandomState(7)
+    bf16 = X.dtype == torch.bfloat16
+    hw = (h.bfloat16() if bf16 else h).double()                       # the weights as the tensor cores see them
+    ridx = torch.from_numpy(np.sort(rs.choice(M, rows, replace=False))).to(DEV)
+    Xs, dYs = X[ridx].double(), dY[ridx].double()
+    # forward: all of K, a few column tiles
+    ns = np.concatenate([np.arange(t * BN, min(N, (t + 1) * BN)) for t in np.sort(rs.choice(-(-N // BN), 3, replace=False))])
+    idx = torch.from_numpy(o.element_index_block(K, N, H, BK, BN, R, mode, np.arange(K), ns)).to(DEV)
+    want = alpha * (Xs @ hw[idx])
+    assert rel(got["fwd"][ridx][:, torch.from_numpy(ns).to(DEV)].float(), want) < TOL_TC
+    # input gradient: all of N, a few row tiles of the virtual weight
+    ks = np.concatenate([np.arange(t * BK, min(K, (t + 1) * BK)) for t in np.sort(rs.choice(-(-K // BK), 3, replace=False))])
+    idx = torch.from_numpy(o.element_index_block(K, N, H, BK, BN, R, mode, ks, np.arange(N))).to(DEV)
+    want = alpha * (dYs @ hw[idx].t())
+    assert rel(got["dx"][ridx][:, torch.from_numpy(ks).to(DEV)].float(), want) < TOL_TC
+    # hashed-weight gradient: sampled words, every virtual element that lands on them, all rows
+    js = np.sort(rs.choice(H, words, replace=False))
+    pairs = [o.elements_of_word(int(j), K, N, H, BK, BN, R, mode) for j in js]
+    owner = np.concatenate([np.full(len(k), i) for i, (k, _) in enumerate(pairs)])
+    kall = torch.from_numpy(np.concatenate([k for k, _ in pairs])).to(DEV)
+    nall = torch.from_numpy(np.concatenate([n for _, n in pairs])).to(DEV)
+    dots = torch.empty(len(owner), dtype=torch.float64, device=DEV)
+    for c0 in range(0, len(owner), 1024):                             # M x 1024 fp64 products at a time
+        sl = slice(c0, c0 + 1024)
+        dots[sl] = (X[:, kall[sl]].double() * dY[:, nall[sl]].double()).sum(0)
+    want = torch.zeros(words, dtype=torch.float64, device=DEV).index_add_(0, torch.from_numpy(owner).to(DEV), dots) * alpha
+    assert len(owner) > words                                         # (compression: several elements per word)
+    assert rel(got["dw"][torch.from_numpy(js).to(DEV)], want) < TOL_TC
+
+
 def check_against_fma_kernels(rzlib, pb, pb_ref, X, dY, h, rows=256):
     got = run(rzlib, pb, X, dY, h)
     st, detail = rzlib.device_status()
     assert st == 0, (st, detail)
+    check_against_oracle_sample(pb, X, dY, h, got)
     # forward / input gradient are row-independent: the FMA kernels redo a sample of rows
     idx = torch.randperm(pb.M, generator=torch.Generator().manual_seed(1))[:rows].sort().values.to(DEV)
     R = list(pb.R)

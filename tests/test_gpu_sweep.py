@@ -89,12 +89,14 @@ def test_configs_forced(rzlib, monkeypatch):
     rs = np.random.RandomState(5)
     for config in ("1", "2", "3"):
         monkeypatch.setenv("RZ_TC_CONFIG", config)
+        rzlib.reload_env()          # the knobs are read once; this reads them again
         rs2 = np.random.RandomState(99)
         errs, desc = None, None
         while errs is None:
             errs, desc = one_case(rzlib, rs2, rzlib.PREC_BF16)
         assert max(errs) < 2e-3, (config, errs, desc)
     monkeypatch.delenv("RZ_TC_CONFIG")
+    rzlib.reload_env()
 
 
 @pytest.mark.parametrize("prec_name,tol", [("bf16", 2e-3), ("tf32", 2e-3), ("fp32", 1e-5)])

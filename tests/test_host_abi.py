@@ -24,9 +24,9 @@ def test_library_exports_every_declared_symbol(rzlib):
     assert lib.rz_version() >= 100
 
 
-def _pb(rzlib, M=64, K=128, N=192, H=8192, BK=32, BN=64, R=None, mode=0, io=0, prec=0, alpha=1.0, flags=0):
+def _pb(rzlib, M=64, K=128, N=192, H=8192, BK=32, BN=64, R=None, mode=0, io=0, prec=0, alpha=1.0, flags=0, sm_reserve=0):
     R = R if R is not None else [LARGE_PRIME, 5, 7, 11, 13, 17, 19, 23]
-    return rzlib.make_problem(M, K, N, H, BK, BN, R, mode, io, prec, alpha, flags)
+    return rzlib.make_problem(M, K, N, H, BK, BN, R, mode, io, prec, alpha, flags, sm_reserve)
 
 
 CASES = [
@@ -86,6 +86,7 @@ def test_adversarial_collisions(rzlib):
     (dict(mode=2), -6), (dict(R=[0, 1, 2, 3, 4, 5, 6, 7]), -6), (dict(R=[7, -1, 2, 3, 4, 5, 6, 7]), -6),
     (dict(R=[7, 1 << 31, 2, 3, 4, 5, 6, 7]), -6),
     (dict(io=2), -4), (dict(prec=3), -4), (dict(io=1, prec=1), -4), (dict(io=0, prec=2), -4),
+    (dict(sm_reserve=-1), -2),
 ])
 def test_validation_statuses(rzlib, kw, status):
     pb = _pb(rzlib, **kw)
@@ -100,8 +101,8 @@ def test_null_pointers_are_rejected_before_any_launch(rzlib):
     lib = rzlib.load()
     pb = _pb(rzlib)
     assert lib.rz_hash_indices_host(ctypes.byref(pb), None) == -1
-    assert lib.rz_linear_forward(ctypes.byref(pb), None, None, None, None, None, None) == -1
-    assert lib.rz_linear_backward_input(ctypes.byref(pb), None, None, None, None, None) == -1
+    assert lib.rz_linear_forward(ctypes.byref(pb), None, None, None, 0, None, None, None) == -1
+    assert lib.rz_linear_backward_input(ctypes.byref(pb), None, None, None, 0, None, None) == -1
     assert lib.rz_linear_backward_weight(ctypes.byref(pb), None, None, None, None) == -1
     assert lib.rz_linear_materialize(ctypes.byref(pb), None, None, None) == -1
     assert lib.rz_grad_prepare(ctypes.byref(pb), None, None, None, None, None) == -1
@@ -123,11 +124,35 @@ def test_plan_selects_kernel_family(rzlib):
         assert rzlib.plan(_pb(rzlib, io=1, prec=2, **big), op) == rzlib.PATH_TCGEN05
         assert rzlib.plan(_pb(rzlib, io=0, prec=1, M=16384, K=4096, N=4096, H=1 << 20, BK=64, BN=64), op) == rzlib.PATH_TCGEN05
     assert rzlib.plan(_pb(rzlib, io=1, prec=2, flags=rzlib.FLAG_FORCE_SIMT, **big), 0) == rzlib.PATH_SIMT
+    # the module's default hash tile (32 x 64, the reference's BLOCK_SIZE_K / BLOCK_SIZE_N) runs on the tensor
+    # cores in every precision: a bf16 pipeline stage of 64 contraction rows is then made of two hash tiles
+    for op in (0, 1, 2):
+        assert rzlib.plan(_pb(rzlib, io=1, prec=2, M=1024, K=1024, N=1024, H=65536, BK=32, BN=64), op) == rzlib.PATH_TCGEN05
+        assert rzlib.plan(_pb(rzlib, io=0, prec=1, M=1024, K=1024, N=1024, H=65536, BK=32, BN=64), op) == rzlib.PATH_TCGEN05
     # hash tiles narrower than a 128-byte row, or odd leading dimensions, fall to the FMA kernels
     assert rzlib.plan(_pb(rzlib, io=1, prec=2, M=1024, K=1024, N=1024, H=65536, BK=32, BN=32), 0) == rzlib.PATH_SIMT
+    assert rzlib.plan(_pb(rzlib, io=1, prec=2, M=1024, K=1024, N=1024, H=65536, BK=48, BN=64), 0) == rzlib.PATH_SIMT
     assert rzlib.plan(_pb(rzlib, io=1, prec=2, M=1024, K=1020, N=1024, H=1 << 20, BK=64, BN=64), 0) == rzlib.PATH_SIMT
     # shadow scratch: NS shifted copies (8 for bf16, 4 for tf32), none for the FMA kernels
     assert rzlib.shadow_bytes(_pb(rzlib, io=1, prec=2, **big)) == 8 * (1 << 22) * 2
     assert rzlib.shadow_bytes(_pb(rzlib, io=0, prec=1, M=16384, K=4096, N=4096, H=1 << 20, BK=64, BN=64)) == 4 * (1 << 20) * 4
     assert rzlib.shadow_bytes(_pb(rzlib, flags=rzlib.FLAG_FORCE_SIMT)) == 0
     assert rzlib.shadow_bytes(_pb(rzlib, BK=16)) == 0
+
+
+def test_scratch_size_rules(rzlib):
+    # the scratch = shifted copies + the workspace of split-contraction launches, which depends on the rows of the
+    # launch and on the SMs it may use: a buffer that serves several problems must be sized for the largest
+    big = dict(io=1, prec=2, K=8192, N=8192, H=1 << 22, BK=128, BN=128)
+    copies = 8 * (1 << 22) * 2
+    assert rzlib.shadow_bytes(_pb(rzlib, M=131072, **big)) == copies                      # full waves only
+    small = rzlib.shadow_bytes(_pb(rzlib, M=128, **big))
+    assert small > copies                                                                  # few blocks: split contraction
+    assert rzlib.shadow_bytes(_pb(rzlib, M=7232, **big)) > rzlib.shadow_bytes(_pb(rzlib, M=40000, **big)) > copies
+    # reserving SMs changes the wave structure, hence possibly the workspace
+    assert rzlib.shadow_bytes(_pb(rzlib, M=16384, sm_reserve=8, **big)) >= copies
+    # copying a problem and changing fields
+    pb = _pb(rzlib, M=40000, **big)
+    q = rzlib.with_fields(pb, M=7232, flags=rzlib.FLAG_ACCUMULATE_DH)
+    assert (q.M, q.K, q.H, q.flags, list(q.R)) == (7232, 8192, 1 << 22, 1, list(pb.R)) and pb.M == 40000
+    assert rzlib.load().rz_status_string(-11).decode().startswith("scratch buffer smaller")

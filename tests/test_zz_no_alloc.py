@@ -60,13 +60,57 @@ def test_noalloc_forward_matches_forward_twice_in_a_row(rzlib, dtype):
 
 def test_noalloc_rejects_problems_beyond_the_fixed_scratch(rzlib):
     pb, X, h, bias = _case(rzlib, 256, 512, 512, (1 << 20) + 64, 128, 128, torch.bfloat16, 3)
-    assert rzlib.shadow_bytes(pb) > rzlib.NOALLOC_SCRATCH_BYTES
+    assert 8 * 2 * ((1 << 20) + 64) > rzlib.NOALLOC_SCRATCH_BYTES     # the shifted copies alone do not fit
     Y = torch.zeros((256, 512), dtype=torch.bfloat16, device=DEV)
     with pytest.raises(rzlib.RzLinearError) as e:
         rzlib.forward_noalloc(pb, X, h, bias, Y)
     assert e.value.status == -10 and "capacity" in str(e.value)
     torch.cuda.synchronize()
     assert float(Y.float().abs().sum()) == 0.0      # nothing was launched
+
+
+def test_noalloc_runs_without_the_workspace_when_only_the_copies_fit(rzlib):
+    # few output blocks and a long contraction: the ordinary entry point splits the contraction and keeps fp32
+    # partial sums in a workspace behind the copies.  Here the copies nearly fill the fixed array, so the
+    # no-alloc call runs whole contractions per block instead: same result up to summation order.
+    H = (1 << 20) - 64
+    pb, X, h, bias = _case(rzlib, 32, 4096, 4096, H, 64, 64, torch.bfloat16, 5)
+    copies = 8 * 2 * H
+    assert copies <= rzlib.NOALLOC_SCRATCH_BYTES < rzlib.shadow_bytes(pb)
+    want = _reference_forward(rzlib, pb, X, h, bias)
+    for _ in range(2):
+        got = torch.zeros_like(want)
+        rzlib.forward_noalloc(pb, X, h, bias, got)
+        torch.cuda.synchronize()
+        err = float((got.float() - want.float()).norm() / want.float().norm())
+        assert err < 2e-3, err                                # the tolerance of the bf16 tensor-core tests
+    # with room for both, the no-alloc call uses the workspace like the ordinary one: bit-identical
+    pb2, X2, h2, bias2 = _case(rzlib, 32, 4096, 4096, 300007, 64, 64, torch.bfloat16, 6)
+    assert 8 * 2 * 300032 < rzlib.shadow_bytes(pb2) <= rzlib.NOALLOC_SCRATCH_BYTES
+    want2 = _reference_forward(rzlib, pb2, X2, h2, bias2)
+    got2 = torch.empty_like(want2)
+    rzlib.forward_noalloc(pb2, X2, h2, bias2, got2)
+    torch.cuda.synchronize()
+    assert torch.equal(got2, want2)
+    assert rzlib.device_status() == (0, 0)
+
+
+def test_noalloc_refuses_fp32_precision_that_needs_its_workspace(rzlib):
+    # fp32 precision bounds its accumulation chains by splitting contractions longer than 2048: without room for
+    # the workspace the call is refused rather than run at lower accuracy
+    rs = np.random.RandomState(8)
+    R = [PRIME] + [int(v) for v in rs.randint(1, 2**31 - 1, 7)]
+    H = (1 << 20) - 64
+    pb = rzlib.make_problem(256, 4096, 1024, H, 64, 64, R, rzlib.HASH_SINGLE, rzlib.F32, rzlib.PREC_FP32, 1.0)
+    assert rzlib.plan(pb, 0) == rzlib.PATH_TCGEN05 and rzlib.shadow_bytes(pb) > rzlib.NOALLOC_SCRATCH_BYTES
+    X = torch.randn(256, 4096, device=DEV)
+    h = torch.rand(H, device=DEV)
+    Y = torch.zeros(256, 1024, device=DEV)
+    with pytest.raises(rzlib.RzLinearError) as e:
+        rzlib.forward_noalloc(pb, X, h, None, Y)
+    assert e.value.status == rzlib.RZ_ERR_TOO_LARGE
+    torch.cuda.synchronize()
+    assert float(Y.abs().sum()) == 0.0
 
 
 def test_noalloc_fp32_path_needs_no_scratch(rzlib):
