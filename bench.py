@@ -14,7 +14,11 @@ Prints ONE JSON line.  `value` is virtual-dense TFLOP/s of the whole job (6*M*K*
 the shards resident in HBM; `e2e` is the same step fed from pinned host memory with the copies
 timed; `roofline` is the dominant kernel against the measured bf16 tensor peak; `cpu_baseline` is
 the materialised-weight computation (the CPU oracle) on a bounded sample.  `--impl reference`
-times that CPU path alone.
+times that CPU path alone.  Outside the timed regions rank 0 also records: `checks` (size-independent
+properties of the step's results and, for N > 1, that the replicas' hashed arrays and gradients are
+identical), `module` (the same layer through the drop-in `RzLinear` module and autograd), `configs`
+(the single-layer and MLP baseline configurations next to cuBLAS) and `cycles` (step time x sampled
+SM clock, which compares runs at different clocks).
 """
 import argparse
 import json
@@ -92,7 +96,7 @@ class ClockSampler(threading.Thread):
                             self.reasons.add(name)
                 except Exception:
                     pass
-                time.sleep(0.05)
+                time.sleep(0.005)
         except Exception as e:  # NVML missing: report what we know
             self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
 
@@ -127,6 +131,13 @@ def cpu_reference_step(Ms: int, threads: int, repeats: int = 1):
     return best
 
 
+def bench_config(m_global, rows_per_gpu, world):
+    """The `config` object of the JSON line (the same for both arms)."""
+    return {"workload": WORKLOAD if m_global == M_GLOBAL else WORKLOAD + f" (m_global={m_global})",
+            "rows_per_gpu": rows_per_gpu, "parallelism": f"dp{world}",
+            "l2": "inputs larger than L2 (X and dY shards are >= 256 MiB each)"}
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -145,12 +156,90 @@ def run_reference(args, rank):
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
+        "config": bench_config(M_GLOBAL, -(-M_GLOBAL // max(1, args.gpus)), max(1, args.gpus)),
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def mcycles(ms, clocks):
+    """Millions of SM cycles per step: time x median sampled SM clock (comparable between runs at different clocks)."""
+    if isinstance(clocks, dict) and clocks.get("sm_mhz"):
+        return ms * float(clocks["sm_mhz"]) / 1000.0
+    return None
+
+
+def run_checks(step, X, dY, world, dev):
+    """One extra step whose results are checked through properties that hold at any size (no oracle involved):
+    the sum of the hashed-weight gradient equals sum_m (sum_k X[m,k]) (sum_n dY[m,n]) over the whole batch because
+    every element of X^T.dY is added exactly once; the update is hashed -= lr * dH; and with several ranks every
+    replica holds the same gradient and the same hashed array, bit for bit."""
+    import torch.distributed as dist
+    h_before = step.hashed.clone()
+    step.step(X, dY)
+    torch.cuda.synchronize()
+    want = (X.sum(1, dtype=torch.float64) * dY.sum(1, dtype=torch.float64)).sum().reshape(1)
+    if world > 1:
+        dist.all_reduce(want, op=dist.ReduceOp.SUM)
+    got = step.dH.double().sum()
+    scale = step.dH.double().abs().sum()
+    upd = (step.hashed.double() - (h_before.double() - step.lr * step.dH.double())).abs().max()
+    out = {"dH_sum_rel_err": float((got - want[0]).abs() / scale),
+           "sgd_update_max_abs_err": float(upd),
+           "finite": bool(torch.isfinite(step.Y.float()).all() and torch.isfinite(step.dX.float()).all()),
+           "replicas_identical": None}
+    if world > 1:
+        # exact checksums: the arrays' bit patterns summed as 64-bit integers, min and max over the ranks
+        sums = torch.stack([step.hashed.view(torch.int32).to(torch.int64).sum(),
+                            step.dH.view(torch.int32).to(torch.int64).sum()])
+        lo, hi = sums.clone(), sums.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        out["replicas_identical"] = bool(torch.equal(lo, hi))
+    out["ok"] = bool(out["dH_sum_rel_err"] < 1e-4 and out["sgd_update_max_abs_err"] < 1e-6 and out["finite"]
+                     and out["replicas_identical"] in (None, True))
+    return out
+
+
+def measure_module(M, R, h0, X, dY, dev, reps):
+    """The same layer through the drop-in API: RzLinear (bias-free, single-level hash, 128 x 128 tile) + autograd,
+    forward and backward (input and hashed-weight gradients) per repetition, timed with CUDA events."""
+    from rzlinear_b200 import RzLinear
+    layer = RzLinear(K, N, hashed_weight=torch.nn.Parameter(h0.to(dev).clone()), bias=False, hash_mode="single",
+                     random_numbers=R, block_size_k=BK, block_size_n=BN).to(dev)
+    Xg = X.detach().requires_grad_(True)
+
+    def one():
+        Xg.grad = None
+        layer._hashed_weight.grad = None
+        layer(Xg).backward(dY)
+
+    for _ in range(3):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    Xg.grad = None
+    return {"ms_fwd_bwd": ms, "tflops": 6.0 * M * K * N / (ms * 1e-3) / 1e12,
+            "api": "RzLinear(...)(X).backward(dY): forward + input gradient + hashed-weight gradient through autograd"}
+
+
+def measure_configs(reps):
+    """The single-layer and MLP baseline configurations, each next to cuBLAS (torch.matmul / nn.Linear on dense
+    weights of the same shape), one GPU, rank 0, outside the timed region of `value`."""
+    from rzlinear_b200 import bench_shapes
+    out = {}
+    for i, (prec, M, Kc, Nc, Hc, bk, bn) in enumerate(bench_shapes.BASELINE):
+        out[f"config{i + 1}"] = bench_shapes.measure(prec, M, Kc, Nc, Hc, bk, bn, reps)
+    out["config4"] = bench_shapes.measure_mlp(reps)
+    return out
 
 
 def main():
@@ -163,6 +252,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the module and baseline-configuration measurements")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -210,7 +300,7 @@ def main():
     step.load_weights(h0.to(dev))
     torch.cuda.synchronize()
 
-    names = ["forward", "backward_weight", "backward_input", "sgd"]
+    names = ["forward", "backward_weight", "backward_input", "comm_wait", "sgd"]
     events = []
 
     def marks_for(slot):
@@ -228,23 +318,36 @@ def main():
     for _ in range(args.warmup):
         step.step(X, dY)
     barrier()
-    launches0 = _lib.launch_count()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    t_start = torch.cuda.Event(enable_timing=True)
-    t_end = torch.cuda.Event(enable_timing=True)
-    t_start.record()
-    for _ in range(args.steps):
-        slot = []
-        step.step(X, dY, marks_for(slot))
-        events.append(slot)
-    t_end.record()
-    barrier()
-    clocks = sampler.stop()
-    launches = _lib.launch_count() - launches0
-    st, detail = _lib.device_status()
-    assert st == 0, f"device pipeline status {st} (wait code {detail})"
-    ms_total = t_start.elapsed_time(t_end)
+
+    # ---- checks on the warmed-up step (outside the timed region) ----
+    checks = run_checks(step, X, dY, world, dev)
+
+    def timed(n_steps, with_marks):
+        """n_steps steps between two events, clocks sampled meanwhile; returns (ms per step max over ranks, clocks,
+        launches, per-step event lists)."""
+        slots = []
+        launches0 = _lib.launch_count()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        t_start = torch.cuda.Event(enable_timing=True)
+        t_end = torch.cuda.Event(enable_timing=True)
+        t_start.record()
+        for _ in range(n_steps):
+            slot = []
+            step.step(X, dY, marks_for(slot) if with_marks else None)
+            slots.append(slot)
+        t_end.record()
+        barrier()
+        clk = sampler.stop()
+        n_launch = _lib.launch_count() - launches0
+        st, detail = _lib.device_status()
+        assert st == 0, f"device pipeline status {st} (wait code {detail})"
+        t = torch.tensor([t_start.elapsed_time(t_end)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / n_steps, clk, n_launch, slots
+
+    ms_step, clocks, launches, events = timed(args.steps, True)
 
     per_kernel = {n: 0.0 for n in names}
     for slot in events:
@@ -252,12 +355,17 @@ def main():
             per_kernel[n1] += e0.elapsed_time(e1)
     per_kernel = {n: v / args.steps for n, v in per_kernel.items()}
 
-    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
     flops_step = 6.0 * m_global * K * N
     value = flops_step / (ms_step * 1e-3) / 1e12
+
+    # A region shorter than half a second runs at boost clocks the power cap would not sustain: a second, longer
+    # repeat (about a second and a half) is reported beside it.
+    long_repeat = None
+    if ms_step * args.steps < 500.0:
+        n_long = min(2000, int(1500.0 / ms_step) + 1)
+        ms_long, clocks_long, _, _ = timed(n_long, False)
+        long_repeat = {"steps": n_long, "ms_per_step": ms_long, "value": flops_step / (ms_long * 1e-3) / 1e12,
+                       "clocks": clocks_long, "mcycles_per_step": mcycles(ms_long, clocks_long)}
 
     # ---- end to end: the same step fed from pinned host buffers, copies inside the timed region ----
     e2e = None
@@ -268,7 +376,7 @@ def main():
         dYh.copy_(dY)
         hh = torch.empty(H, dtype=torch.float32).pin_memory()
         torch.cuda.synchronize()
-        e_steps = max(2, min(args.steps, 5))
+        e_steps = args.steps
         for _ in range(2):
             step.step_host(Xh, dYh, hh)
         barrier()
@@ -319,6 +427,19 @@ def main():
                   "what": "torch.matmul bf16 on a dense W[K,N]: X@W, dY@W^T, X^T@dY, back to back per GEMM"}
         del Wd, dWd
 
+    # ---- the drop-in module on this workload, and the other baseline configurations (rank 0) ----
+    module = configs = None
+    if rank == 0 and not args.no_configs:
+        del step.Y, step.dX                      # (the module path allocates its own outputs)
+        torch.cuda.empty_cache()
+        module = measure_module(M, R, h0, X, dY, dev, max(3, min(args.steps, 10)))
+        direct = per_kernel["forward"] + per_kernel["backward_weight"] + per_kernel["backward_input"]
+        module["direct_ms_fwd_bwd"] = direct
+        module["module_over_direct"] = module["ms_fwd_bwd"] / direct
+        del X, dY
+        torch.cuda.empty_cache()
+        configs = measure_configs(10)
+
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         dom = max(("forward", "backward_weight", "backward_input"), key=lambda n: per_kernel[n])
@@ -328,32 +449,40 @@ def main():
         # at N = 1, 2), the burst figure when the step was short enough to run at full clocks (N = 4, 8).
         capped = True
         if isinstance(clocks, dict) and clocks.get("sm_mhz") and clocks.get("sm_max_mhz"):
-            capped = ("sw_power_cap" in (clocks.get("reasons") or [])) or clocks["sm_mhz"] < 0.9 * clocks["sm_max_mhz"]
+            capped = clocks["sm_mhz"] < 0.9 * clocks["sm_max_mhz"]     # (the sampled clock decides, not the reason flags)
         peak_key = "bf16_tflops_sustained" if capped else "bf16_tflops"
         peak = float(peaks.get(peak_key, peaks.get("bf16_tflops")))
         roofline = {"bound": "tensor", "kernel": f"rz_tc_kernel<{dom}>", "achieved": achieved, "peak": peak,
                     "unit": "TFLOP/s", "frac": achieved / peak, "traffic": DRAM_BYTES_PER_ROW[dom] * M,
                     "traffic_source": "ncu dram bytes of the 8192-row case scaled by rows",
-                    "peak_source": f"{peak_kind} {peak_key} (" + ("kernel timed inside a long, power-capped step)"
-                                                                   if capped else "step short enough to run at full clocks)"),
+                    "peak_source": f"{peak_kind} {peak_key} (" + ("sampled SM clock below 0.9 of max: sustained figure)"
+                                                                   if capped else "sampled SM clock at 0.9 of max or above: burst figure)"),
                     "ms_per_launch": per_kernel[dom]}
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD if m_global == M_GLOBAL else WORKLOAD + f" (m_global={m_global})",
-                       "rows_per_gpu": M, "parallelism": f"dp{world}",
-                       "l2": "inputs larger than L2 (X and dY shards are >= 256 MiB each)"},
+            "config": bench_config(m_global, M, world),
             "per_gpu_tflops": value / world,
             "kernel_ms": per_kernel,
             "kernel_tflops": {n: flops_kernel / (per_kernel[n] * 1e-3) / 1e12
                               for n in ("forward", "backward_weight", "backward_input")},
             "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches),
+            "comm_exposed_ms": per_kernel["comm_wait"],
+            "cycles": {"mcycles_per_step": mcycles(ms_step, clocks),
+                       "what": "ms_per_step x median sampled SM MHz / 1000: millions of SM cycles per step"},
+            "checks": checks,
         }
+        if long_repeat is not None:
+            line["long_repeat"] = long_repeat
         if e2e is not None:
             line["e2e"] = e2e
         if cublas is not None:
             line["cublas"] = cublas
+        if module is not None:
+            line["module"] = module
+        if configs is not None:
+            line["configs"] = configs
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
             Ms = 4096

@@ -8,6 +8,8 @@ the same shape as the comparison line; once with tf32 tensor cores allowed and o
     python -m rzlinear_b200.bench_shapes --baseline          # the single-layer and MLP baseline configurations
     python -m rzlinear_b200.bench_shapes --dtype bf16 --shape 128,10240,10240 [--hashed H --block BK,BN]
 
+The hash tile defaults to the reference's 32 x 64 in every precision.
+
 Prints one JSON line per shape and precision.
 """
 from __future__ import annotations
@@ -44,16 +46,16 @@ BASELINE = [("fp32", 1024, 1024, 1024, 65536, 32, 32),
             ("bf16", 8192, 8192, 32768, 1 << 22, 128, 128)]
 
 
-def run(precision: str, reps: int, block_k: int = 32, block_n: int = 64, device="cuda:0", shapes=None, hashed=None):
+def measure(precision: str, M: int, K: int, N: int, H: int, block_k: int, block_n: int, reps: int, device="cuda:0") -> dict:
+    """forward / hashed-weight gradient / input gradient of one shape through the C ABI, and torch.matmul on a dense
+    weight of the same shape (the reference's comparison line, python/bench/bench.py:40-42,78-79,120-121)."""
     dev = torch.device(device)
     dtype = torch.bfloat16 if precision == "bf16" else torch.float32
     prec = {"fp32": _lib.PREC_FP32, "tf32": _lib.PREC_TF32, "bf16": _lib.PREC_BF16}[precision]
-    if precision == "bf16" and shapes is None:
-        block_k = max(block_k, 64)
+    was_tf32 = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = precision == "tf32"
-    R = [PRIME] + [int(v) for v in np.random.RandomState(0).randint(1, 2**31 - 1, 7)]
-    for (M, K, N) in (shapes or CONFIGS):
-        H = hashed or int(K * N * 0.0625)           # default: the reference's default compress_ratio
+    try:
+        R = [PRIME] + [int(v) for v in np.random.RandomState(0).randint(1, 2**31 - 1, 7)]
         pb = _lib.make_problem(M, K, N, H, block_k, block_n, R, _lib.HASH_SINGLE, _lib.torch_io_dtype(dtype), prec)
         g = torch.Generator(device=dev).manual_seed(0)
         X = torch.randn((M, K), generator=g, device=dev).to(dtype)
@@ -76,13 +78,25 @@ def run(precision: str, reps: int, block_k: int = 32, block_n: int = 64, device=
             "cublas_backward_weight": _time(lambda: torch.matmul(X.t(), dY, out=dW), reps),
             "cublas_backward_input": _time(lambda: torch.matmul(dY, W.t(), out=dX), reps),
         }
-        tflops = {k: 2.0 * M * N * K * 1e-12 / (v * 1e-3) for k, v in ms.items()}
-        print(json.dumps({"precision": precision, "M": M, "K": K, "N": N, "H": H, "block": [block_k, block_n],
-                          "path": "tcgen05" if _lib.plan(pb, 0) == _lib.PATH_TCGEN05 else "fma",
-                          "tflops": {k: round(v, 2) for k, v in tflops.items()}}), flush=True)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = was_tf32
+    tflops = {k: 2.0 * M * N * K * 1e-12 / (v * 1e-3) for k, v in ms.items()}
+    ours = ms["forward"] + ms["backward_weight"] + ms["backward_input"]
+    dense = ms["cublas_forward"] + ms["cublas_backward_weight"] + ms["cublas_backward_input"]
+    return {"precision": precision, "M": M, "K": K, "N": N, "H": H, "block": [block_k, block_n],
+            "path": "tcgen05" if _lib.plan(pb, 0) == _lib.PATH_TCGEN05 else "fma",
+            "tflops": {k: round(v, 2) for k, v in tflops.items()},
+            "fwd_bwd_tflops": round(6.0 * M * N * K * 1e-12 / (ours * 1e-3), 2),
+            "pct_of_cublas": round(100.0 * dense / ours, 1)}
 
 
-def run_mlp(reps: int, batch: int = 65536, dims=(1024, 4096, 4096, 256), hashed: int = 1 << 18, device="cuda:0"):
+def run(precision: str, reps: int, block_k: int = 32, block_n: int = 64, device="cuda:0", shapes=None, hashed=None):
+    for (M, K, N) in (shapes or CONFIGS):
+        H = hashed or int(K * N * 0.0625)           # default: the reference's default compress_ratio
+        print(json.dumps(measure(precision, M, K, N, H, block_k, block_n, reps, device)), flush=True)
+
+
+def measure_mlp(reps: int, batch: int = 65536, dims=(1024, 4096, 4096, 256), hashed: int = 1 << 18, device="cuda:0") -> dict:
     """Full training step (forward, MSE loss, backward) of the 3-layer ReLU MLP baseline configuration in bf16,
     next to the same MLP built from dense torch.nn.Linear layers (cuBLAS).  The input needs no gradient, so the
     step runs 3 forward, 3 weight-gradient and 2 input-gradient products."""
@@ -114,8 +128,13 @@ def run_mlp(reps: int, batch: int = 65536, dims=(1024, 4096, 4096, 256), hashed:
 
     flops = 2.0 * batch * (3 * sum(dims[i] * dims[i + 1] for i in range(3)) - dims[0] * dims[1])
     ms = {"rz_mlp_step": _time(step_ours, reps), "dense_mlp_step": _time(step_dense, reps)}
-    print(json.dumps({"config": "mlp", "batch": batch, "dims": list(dims), "H": hashed, "ms": {k: round(v, 3) for k, v in ms.items()},
-                      "tflops": {k: round(flops * 1e-12 / (v * 1e-3), 1) for k, v in ms.items()}}), flush=True)
+    return {"config": "mlp", "batch": batch, "dims": list(dims), "H": hashed, "ms": {k: round(v, 3) for k, v in ms.items()},
+            "tflops": {k: round(flops * 1e-12 / (v * 1e-3), 1) for k, v in ms.items()},
+            "pct_of_dense": round(100.0 * ms["dense_mlp_step"] / ms["rz_mlp_step"], 1)}
+
+
+def run_mlp(reps: int, **kw):
+    print(json.dumps(measure_mlp(reps, **kw)), flush=True)
 
 
 if __name__ == "__main__":
@@ -125,7 +144,7 @@ if __name__ == "__main__":
     ap.add_argument("--baseline", action="store_true", help="run the baseline configurations instead of the sweep")
     ap.add_argument("--shape", default=None, help="M,K,N: one shape instead of the sweep")
     ap.add_argument("--hashed", type=int, default=None, help="length of the hashed array (default K*N/16)")
-    ap.add_argument("--block", default=None, help="BK,BN hash tile (default 32,64; 64,64 for bf16)")
+    ap.add_argument("--block", default=None, help="BK,BN hash tile (default 32,64)")
     a = ap.parse_args()
     if a.baseline:
         for (prec, M, K, N, H, bk, bn) in BASELINE:
@@ -135,6 +154,4 @@ if __name__ == "__main__":
         shapes = [tuple(int(v) for v in a.shape.split(","))] if a.shape else None
         bk, bn = (int(v) for v in a.block.split(",")) if a.block else (32, 64)
         for p in (["tf32", "fp32", "bf16"] if a.dtype == "all" else [a.dtype]):
-            if shapes and not a.block and p == "bf16":
-                bk = 64
             run(p, a.reps, bk, bn, shapes=shapes, hashed=a.hashed)
