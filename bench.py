@@ -203,31 +203,47 @@ def run_checks(step, X, dY, world, dev):
     return out
 
 
-def measure_module(M, R, h0, X, dY, dev, reps):
+def measure_module(step, M, R, h0, X, dY, dev, reps):
     """The same layer through the drop-in API: RzLinear (bias-free, single-level hash, 128 x 128 tile) + autograd,
-    forward and backward (input and hashed-weight gradients) per repetition, timed with CUDA events."""
+    forward and backward (input and hashed-weight gradients) per repetition, timed with CUDA events - and, under the
+    same conditions (alternating with it, so that both see the same clocks), the three kernels called directly."""
     from rzlinear_b200 import RzLinear
     layer = RzLinear(K, N, hashed_weight=torch.nn.Parameter(h0.to(dev).clone()), bias=False, hash_mode="single",
                      random_numbers=R, block_size_k=BK, block_size_n=BN).to(dev)
     Xg = X.detach().requires_grad_(True)
+    k = step.kernels
 
-    def one():
+    def through_module():
         Xg.grad = None
         layer._hashed_weight.grad = None
         layer(Xg).backward(dY)
 
+    def direct():
+        k.forward(X, step.hashed, step.Y)
+        k.backward_weight(X, dY, step.dH)
+        k.backward_input(dY, step.hashed, step.dX)
+
+    def timed(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
     for _ in range(3):
-        one()
+        through_module()
+        direct()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        one()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / reps
+    ms_mod, ms_dir = [], []
+    for _ in range(3):
+        ms_mod.append(timed(through_module))
+        ms_dir.append(timed(direct))
     Xg.grad = None
-    return {"ms_fwd_bwd": ms, "tflops": 6.0 * M * K * N / (ms * 1e-3) / 1e12,
+    ms, ms_d = statistics.median(ms_mod), statistics.median(ms_dir)
+    return {"ms_fwd_bwd": ms, "tflops": 6.0 * M * K * N / (ms * 1e-3) / 1e12, "direct_ms_fwd_bwd": ms_d,
+            "module_over_direct": ms / ms_d, "reps": f"median of 3 x {reps}, module and direct calls alternating",
             "api": "RzLinear(...)(X).backward(dY): forward + input gradient + hashed-weight gradient through autograd"}
 
 
@@ -430,13 +446,8 @@ def main():
     # ---- the drop-in module on this workload, and the other baseline configurations (rank 0) ----
     module = configs = None
     if rank == 0 and not args.no_configs:
-        del step.Y, step.dX                      # (the module path allocates its own outputs)
-        torch.cuda.empty_cache()
-        module = measure_module(M, R, h0, X, dY, dev, max(3, min(args.steps, 10)))
-        direct = per_kernel["forward"] + per_kernel["backward_weight"] + per_kernel["backward_input"]
-        module["direct_ms_fwd_bwd"] = direct
-        module["module_over_direct"] = module["ms_fwd_bwd"] / direct
-        del X, dY
+        module = measure_module(step, M, R, h0, X, dY, dev, max(3, min(args.steps, 10)))
+        del step.Y, step.dX, X, dY
         torch.cuda.empty_cache()
         configs = measure_configs(10)
 

@@ -4,9 +4,17 @@ and at the configuration's full size (1024 -> 4096 -> 4096 -> 256, batch 65536, 
 with the reference's own method - torch matmuls over the materialised weight on the GPU
 (python/tests/test_rz_linear.py:68-71), fp32, the weight gathered with the oracle's index table.
 
-Bar: loss and all three hashed-weight gradients within 2e-3 (1e-4 in fp32).  In the bf16 case the reference takes
-the same rounding points as the kernels (bf16 weights, bf16 activations and gradients between layers, fp32
-accumulation), so that the comparison isolates the kernels."""
+Two comparisons.  (1) Layer by layer on the tensors the kernels themselves saw (captured with module hooks): each
+layer's output, input gradient, hashed-weight gradient and bias gradient against the reference computed from that
+layer's own input and incoming gradient - identical rounding points by construction; bar 2e-3 (1e-4 in fp32).
+(2) End to end against an independent run of the whole network with the same rounding points (bf16 weights, bf16
+activations and gradients between layers, fp32 accumulation): loss and hashed-weight gradients within 2e-3
+(1e-4 in fp32), except the first layer's at full size in bf16.  There the two runs no longer see the same numbers:
+two fp32-accumulating implementations round about 3e-4 of layer 0's outputs to different bf16 neighbours, each
+product multiplies that fraction (0.8 % after layer 1, 7 % after layer 2, 19 % of the gradient that arrives back at
+layer 0 - measured), and layer 0's gradient is a sum with heavy cancellation, so those one-ulp differences show as
+3.4e-3 of its norm.  Any two independent implementations differ like that; comparison (1) shows it is not the
+kernels (layer 0's gradient from its own inputs: 3e-5).  The end-to-end bar for that one gradient is 1e-2."""
 import numpy as np
 import pytest
 import torch
@@ -31,7 +39,12 @@ def build_layers(dims, H, BK, BN):
     return layers
 
 
-def run_case(dims, batch, H, BK, BN, dtype, tol, ref_dev):
+def rel(a, b):
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm())
+
+
+def run_case(dims, batch, H, BK, BN, dtype, tol, ref_dev, tol_first_layer=None):
     layers = build_layers(dims, H, BK, BN)
     model = torch.nn.Sequential(*layers).to(DEV)
     g = torch.Generator().manual_seed(0)
@@ -41,24 +54,59 @@ def run_case(dims, batch, H, BK, BN, dtype, tol, ref_dev):
         with torch.no_grad():
             l._bias.copy_(torch.randn(dims[i + 1], generator=g) * 0.1)
 
+    seen = {}
+    for i, l in enumerate(layers):
+        l.register_forward_hook(lambda m, inp, out, i=i: seen.__setitem__(("fwd", i), (inp[0].detach(), out.detach())))
+        l.register_full_backward_hook(lambda m, gin, gout, i=i: seen.__setitem__(
+            ("bwd", i), (gout[0].detach(), None if gin[0] is None else gin[0].detach())))
     out = model(x.to(DEV).to(dtype))
     loss = torch.nn.functional.mse_loss(out.float(), target.to(DEV))
     loss.backward()
     torch.cuda.synchronize()
     from rzlinear_b200 import _lib
     assert _lib.device_status() == (0, 0)
+    assert not torch.backends.cuda.matmul.allow_tf32          # the reference's GEMMs are plain fp32 / fp64
 
     bf = dtype == torch.bfloat16
     wd = torch.float32 if bf else torch.float64
-    assert not torch.backends.cuda.matmul.allow_tf32          # the reference's GEMMs are plain fp32 / fp64
+    index = [torch.from_numpy(o.element_index(dims[i], dims[i + 1], H, BK, BN, l._random_numbers.tolist(), 0)).to(ref_dev)
+             for i, l in enumerate(layers)]
+
+    # (1) layer by layer, from the tensors each layer saw
+    errs = {}
+    for i, l in enumerate(layers):
+        a_in, a_out = (t.to(ref_dev) for t in seen[("fwd", i)])
+        g_out, g_in = seen[("bwd", i)]
+        g_out = g_out.to(ref_dev)
+        h = l._hashed_weight.detach().to(ref_dev).to(wd)
+        W = h[index[i]]
+        if bf:
+            W = W.bfloat16().float()
+        want = a_in.to(wd) @ W + l._bias.detach().to(ref_dev).to(wd)
+        if i < 2:
+            want = torch.relu(want)
+        errs[f"layer{i}.out"] = rel(a_out, want)
+        gm = g_out.to(wd) * (a_out > 0) if i < 2 else g_out.to(wd)
+        G = a_in.to(wd).t() @ gm
+        dH = torch.zeros(H, dtype=wd, device=ref_dev).index_add_(0, index[i].reshape(-1), G.reshape(-1))
+        errs[f"layer{i}.dH"] = rel(l._hashed_weight.grad.to(ref_dev), dH)
+        errs[f"layer{i}.db"] = rel(l._bias.grad.to(ref_dev), gm.sum(0))
+        if g_in is not None:
+            errs[f"layer{i}.dX"] = rel(g_in.to(ref_dev), gm @ W.t())
+    print("mlp, layer by layer", dims, batch, dtype, {k: f"{v:.1e}" for k, v in errs.items()})
+    assert max(errs.values()) < tol, errs
+
+    # (2) end to end
     hs = [l._hashed_weight.detach().to(ref_dev).to(wd).requires_grad_(True) for l in layers]
     bs = [l._bias.detach().to(ref_dev).to(wd).requires_grad_(True) for l in layers]
     a = (x.bfloat16() if bf else x.double()).to(ref_dev)
     for i, l in enumerate(layers):
-        idx = torch.from_numpy(o.element_index(dims[i], dims[i + 1], H, BK, BN, l._random_numbers.tolist(), 0)).to(ref_dev)
-        W = hs[i][idx]
+        W = hs[i][index[i]]
         if bf:
-            a = (a.float() @ W.bfloat16().float() + bs[i])
+            # bf16 weights in the product, but an unrounded gradient: a plain W.bfloat16().float() would make autograd
+            # round the weight gradient to bf16 on its way back, which the kernels (fp32 gradient) do not do
+            Wb = W + (W.bfloat16().float() - W).detach()
+            a = (a.float() @ Wb + bs[i])
         else:
             a = a @ W + bs[i]
         if i < 2:
@@ -71,7 +119,9 @@ def run_case(dims, batch, H, BK, BN, dtype, tol, ref_dev):
     for i, l in enumerate(layers):
         errs[f"dH{i}"] = o.rel_l2(l._hashed_weight.grad.cpu().numpy(), hs[i].grad.cpu().numpy())
         errs[f"db{i}"] = o.rel_l2(l._bias.grad.cpu().numpy(), bs[i].grad.cpu().numpy())
-    print("mlp errors", dims, batch, dtype, {k: f"{v:.2e}" for k, v in errs.items()})
+    print("mlp, end to end", dims, batch, dtype, {k: f"{v:.1e}" for k, v in errs.items()})
+    first = errs.pop("dH0")
+    assert first < (tol_first_layer or tol), first
     assert max(errs.values()) < tol, errs
 
 
@@ -82,4 +132,4 @@ def test_three_layer_mlp_step(dtype, tol):
 
 def test_three_layer_mlp_step_full_size_bf16():
     # the MLP baseline configuration itself; the tensor-core path runs every product (hash tile 64 x 64)
-    run_case([1024, 4096, 4096, 256], 65536, 1 << 18, 64, 64, torch.bfloat16, 2e-3, DEV)
+    run_case([1024, 4096, 4096, 256], 65536, 1 << 18, 64, 64, torch.bfloat16, 2e-3, DEV, tol_first_layer=1e-2)

@@ -307,6 +307,8 @@ def tc_case(rzlib, L, M, K, N, H, BK, BN, dtype, seed, alpha=1.0, mode=0, allow_
     (384, 256, 768, 100003, 64, 128),      # odd H, rectangular tile
     (300, 320, 328, 1 << 16, 64, 64),      # ragged M, K, N (multiples of 8 only)
     (128, 1024, 256, 1 << 18, 256, 64),
+    (256, 512, 512, 1 << 16, 32, 64),      # the module's default hash tile: two hash tiles per 64-row stage
+    (520, 328, 1032, 50001, 32, 128),      # the same, ragged, pair blocks
 ])
 def test_bf16_tensor_core_path(rzlib, L, M, K, N, H, BK, BN):
     eY, eX, eH = tc_case(rzlib, L, M, K, N, H, BK, BN, torch.bfloat16, seed=M + K + BK, alpha=0.75)

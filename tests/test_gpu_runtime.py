@@ -18,12 +18,12 @@ def _problem(rzlib, M, K, N, H, BK, BN, prec, **kw):
 
 
 @pytest.mark.parametrize("prec_name", ["bf16", "tf32", "fp32"])
-@pytest.mark.parametrize("H", [1 << 17, 100003, 64 * 64 + 1, 2055, 3 * 256 * 8 + 5])
+@pytest.mark.parametrize("H", [1 << 17, 100003, 64 * 64 + 1, 2055, 3 * 256 * 8 + 5])   # (2055: one word more than a 32 x 64 tile)
 @pytest.mark.parametrize("momentum", [0.0, 0.9])
 def test_optimiser_step_rewrites_the_shadow_in_the_same_launch(rzlib, prec_name, H, momentum):
     # hashed / velocity against fp64 arithmetic; the shadow bit-identical to a refresh from the updated array
     prec = {"bf16": rzlib.PREC_BF16, "tf32": rzlib.PREC_TF32, "fp32": rzlib.PREC_FP32}[prec_name]
-    BK = BN = 64 if H > 64 * 64 else 32
+    BK, BN = (64, 64) if H > 64 * 64 else (32, 64)
     pb = _problem(rzlib, 256, 256, 256, H, BK, BN, prec)
     assert rzlib.plan(pb, 0) == rzlib.PATH_TCGEN05
     g = torch.Generator().manual_seed(H)

@@ -22,7 +22,7 @@ def one_case(rzlib, rs, prec):
     M = int(rs.choice([8, 32, 72, 128, 136, 200, 256, 384, 520, 640, 1024, 1500]))
     K = int(rs.randint(tile_unit // unit, 96)) * unit
     N = int(rs.randint(tile_unit // unit, 96)) * unit
-    BK = int(rs.choice([tile_unit, 2 * tile_unit, 128, 256]))
+    BK = int(rs.choice([32, 64, 128, 256]))
     BN = int(rs.choice([tile_unit, 2 * tile_unit, 3 * tile_unit, 128, 256]))
     if BK <= 128 and 128 % BK:
         BK = 128

@@ -84,14 +84,17 @@ def test_noalloc_runs_without_the_workspace_when_only_the_copies_fit(rzlib):
         torch.cuda.synchronize()
         err = float((got.float() - want.float()).norm() / want.float().norm())
         assert err < 2e-3, err                                # the tolerance of the bf16 tensor-core tests
-    # with room for both, the no-alloc call uses the workspace like the ordinary one: bit-identical
+    # with room for both, the no-alloc call splits the contraction like the ordinary one (the partial sums meet in
+    # the workspace through atomic adds, so the order of summation, and with it the last bit, varies from run to run)
     pb2, X2, h2, bias2 = _case(rzlib, 32, 4096, 4096, 300007, 64, 64, torch.bfloat16, 6)
     assert 8 * 2 * 300032 < rzlib.shadow_bytes(pb2) <= rzlib.NOALLOC_SCRATCH_BYTES
     want2 = _reference_forward(rzlib, pb2, X2, h2, bias2)
-    got2 = torch.empty_like(want2)
-    rzlib.forward_noalloc(pb2, X2, h2, bias2, got2)
-    torch.cuda.synchronize()
-    assert torch.equal(got2, want2)
+    for _ in range(2):
+        got2 = torch.zeros_like(want2)
+        rzlib.forward_noalloc(pb2, X2, h2, bias2, got2)
+        torch.cuda.synchronize()
+        err = float((got2.float() - want2.float()).norm() / want2.float().norm())
+        assert err < 2e-3, err
     assert rzlib.device_status() == (0, 0)
 
 
