@@ -14,8 +14,6 @@ std::atomic<uint64_t> g_launches{0};
 
 // Device-side status word: 0, or (wait code << 8 | 1) once a bounded wait gave up.  Sticky until rz_device_status().
 __device__ int g_rz_status_word = 0;
-// Epoch of the launch whose wait gave up last: tells that launch's other waiters to leave.
-__device__ unsigned g_rz_abort_epoch = 0;
 
 // Host copy of the status words, one int per device index, in a page of this library that is registered as
 // mapped pinned memory the first time a tensor-core launch is prepared: a kernel whose wait gives up stores its
@@ -27,11 +25,9 @@ bool g_host_registered = false;
 
 struct DeviceAddrs {
     std::atomic<int *> status{nullptr};
-    std::atomic<unsigned *> abort_word{nullptr};
     std::atomic<int *> host{nullptr};
 };
 DeviceAddrs g_addrs[RZ_MAX_DEVICES];
-std::atomic<unsigned> g_epoch{0};
 
 int validate(const rz_problem *pb)
 {
@@ -111,10 +107,7 @@ int rz_wait_context(RzWaitCtx *w, long long limit_cycles)
     DeviceAddrs &a = g_addrs[dev];
     int *status = a.status.load(std::memory_order_acquire);
     if (!status) {   // first launch on this device: the addresses never change while the module is loaded
-        unsigned *abort_word = nullptr;
         st = rz_record_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_rz_status_word), "status word address");
-        if (st) return st;
-        st = rz_record_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(&abort_word), g_rz_abort_epoch), "abort word address");
         if (st) return st;
         std::call_once(g_host_once, [] {
             g_host_registered = cudaHostRegister(g_host_status, sizeof(g_host_status),
@@ -128,17 +121,12 @@ int rz_wait_context(RzWaitCtx *w, long long limit_cycles)
             (void)cudaGetLastError();
         }
         a.host.store(host_dev, std::memory_order_relaxed);
-        a.abort_word.store(abort_word, std::memory_order_relaxed);
         a.status.store(status, std::memory_order_release);
     }
     w->status = status;
-    w->abort_word = a.abort_word.load(std::memory_order_relaxed);
     w->host_status = a.host.load(std::memory_order_relaxed);
     w->limit_cycles = limit_cycles;
     if (w->host_status && *reinterpret_cast<volatile int *>(&g_host_status[dev]) != 0) return RZ_ERR_PIPELINE;
-    unsigned e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
-    if (e == 0) e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;   // 0 is the abort word's idle value
-    w->epoch = e;
     return RZ_OK;
 }
 

@@ -19,17 +19,15 @@ enum RzWaitCode {
 };
 
 // Where a device-side bounded wait reports that it gave up (filled by rz_wait_context):
-//   status      sticky device word, read and cleared by rz_device_status();
-//   host_status host-mapped copy of it (may be NULL) that the host looks at, without synchronising, before
-//               every tensor-core launch, so that work after a failed kernel is refused instead of continuing
-//               on partial results;
-//   abort_word / epoch  tell the other waiters of the SAME launch to leave their loops; a launch reacts only
-//               to its own epoch, so a word left behind by an earlier launch never stops a later one.
+//   status      sticky device word, read and cleared by rz_device_status(); while it is non-zero every bounded wait on
+//               the device gives up at once, so the other roles of the failing kernel leave their loops too;
+//   host_status host-mapped copy of it (NULL when the page could not be pinned) that the host looks at, without
+//               synchronising, before every tensor-core launch: work after a failed kernel is refused
+//               (RZ_ERR_PIPELINE) instead of continuing on partial results, until rz_device_status() has
+//               acknowledged the failure and cleared both words.
 struct RzWaitCtx {
     int *status;
     int *host_status;
-    unsigned *abort_word;
-    unsigned epoch;
     long long limit_cycles;
 };
 
@@ -42,8 +40,8 @@ struct RzLaunchCtx {
 // host helpers (rz_abi.cu)
 int rz_record_cuda(cudaError_t e, const char *what);
 void rz_count_launch(int n);
-// Fills `w` for a launch on the current device (fresh epoch).  RZ_ERR_PIPELINE when an earlier kernel on this
-// device reported a wait that gave up and rz_device_status() has not been called since.
+// Fills `w` for a launch on the current device.  RZ_ERR_PIPELINE when an earlier kernel on this device reported a
+// wait that gave up and rz_device_status() has not been called since.
 int rz_wait_context(RzWaitCtx *w, long long limit_cycles);
 
 // rz_linear_forward with a say on the scratch: `copies_suffice` lets a scratch that holds the shifted copies but not

@@ -89,30 +89,25 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 
 using WaitCtx = RzWaitCtx;   // rz_common.h
 
-__device__ __forceinline__ void wait_give_up(const WaitCtx &w, int code)
-{
-    atomicCAS(w.status, 0, (code << 8) | 1);
-    *reinterpret_cast<volatile unsigned *>(w.abort_word) = w.epoch;
-    if (w.host_status) *reinterpret_cast<volatile int *>(w.host_status) = (code << 8) | 1;
-    __threadfence_system();
-}
-
-// Bounded wait: gives up after `w.limit_cycles` SM cycles (or as soon as another waiter of this launch has given
-// up), records `code` and returns false.  The caller then leaves its loop.
+// Bounded wait: gives up after `w.limit_cycles` SM cycles (or as soon as another waiter has given up), records
+// `code` in the device status word and in its host-mapped copy, and returns false.  The caller then leaves its loop.
 // `hint_ns` > 0 is for waits that are expected to be long (an epilogue waiting for a whole main
 // loop): the thread sleeps in the barrier unit between polls instead of burning issue slots.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int code, const WaitCtx &w,
                                                   uint32_t hint_ns = 0)
 {
     if (mbar_try_wait(bar, parity)) return true;
+    int *status = w.status;
+    const long long limit_cycles = w.limit_cycles;
     const long long t0 = clock64();
     const uint32_t check_mask = hint_ns ? 0x3u : 0xffu;
     for (uint32_t it = 1;; ++it) {
         if (hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity)) return true;
         if ((it & check_mask) == 0) {
-            if (*reinterpret_cast<volatile unsigned *>(w.abort_word) == w.epoch) return false;
-            if (clock64() - t0 > w.limit_cycles) {
-                wait_give_up(w, code);
+            if (*reinterpret_cast<volatile int *>(status) != 0) return false;
+            if (clock64() - t0 > limit_cycles) {
+                atomicCAS(status, 0, (code << 8) | 1);
+                if (w.host_status) *reinterpret_cast<volatile int *>(w.host_status) = (code << 8) | 1;
                 return false;
             }
         }

@@ -102,7 +102,7 @@ struct TcParams {
     void *out;
     float *dH;
     float *ws;                  // FWD / DX with a split contraction: fp32 partial sums [rows][cols]
-    WaitCtx wait;               // where bounded waits report, and this launch's epoch
+    WaitCtx wait;               // where bounded waits report
     uint32_t tma_store;         // FWD / DX: write the output with bulk tensor stores (0 = plain 16-byte stores)
 };
 

@@ -174,6 +174,6 @@ def test_launches_are_refused_after_a_wait_gave_up_until_acknowledged(rzlib):
     assert float(Y.float().abs().sum()) == 0.0                 # refused before anything was launched
     assert rzlib.device_status() == (rzlib.RZ_ERR_PIPELINE, 6)
     assert rzlib.device_status() == (0, 0)
-    rzlib.forward(pb, X, h, shadow, None, Y)                   # acknowledged: back to normal, and the word left behind
-    torch.cuda.synchronize()                                   # by the failed launch does not stop this one
+    rzlib.forward(pb, X, h, shadow, None, Y)                   # acknowledged: back to normal
+    torch.cuda.synchronize()
     assert torch.equal(Y, good) and rzlib.device_status() == (0, 0)
