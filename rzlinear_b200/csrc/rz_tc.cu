@@ -3,7 +3,9 @@
 // One persistent, warp-specialised kernel template covers the three contractions:
 //   OP_FWD  Y [M,N] = X  [M,K] . W[K,N]      A = X tile  (K-major),  B = W slice (N-major)
 //   OP_DX   dX[M,K] = dY [M,N] . W[K,N]^T    A = dY tile (K-major),  B = W slice (K-major)
-//   OP_DW   dH     += X^T[K,M] . dY[M,N]     A = X tile  (M-major),  B = dY tile (N-major)
+//   OP_DW   dH     += dY^T[N,M] . X[M,K]     A = dY tile (M-major),  B = X tile  (N-major): the TRANSPOSE of the
+//                                             weight-gradient block, so that a warp's 32 accumulator rows are 32
+//                                             consecutive words of a slice row and reductions need no transpose
 // CTAS = 1, RB = 1: a CTA owns a 128 x 256 output block (tcgen05.mma cta_group::1, M = 128).
 // CTAS = 2, RB = 1: two CTAs of a cluster own a 256 x 256 block (cta_group::2, M = 256): each CTA
 //           stages its 128 rows of A and its 128 columns of B.  The leader CTA (rank 0) issues the
@@ -58,15 +60,14 @@ constexpr int MAX_TPS = 8;   // B boxes per stage at most
 constexpr int GROUP_ROWS = 8;   // row tiles per rasterisation group (4 when a tile has two row blocks)
 
 // Shared-memory budget (227 KB per CTA): the operand ring takes what the other parts leave.
-// Only the weight-gradient epilogue needs transpose scratch, so FWD / DX get one more 32 KB stage.
-constexpr int SMEM_EPI_WARP = 32 * 33 * 4;
+// The weight-gradient epilogue reduces straight from registers and needs no staging, so its ring gets the space.
 constexpr int SMEM_TABLE = 3 * BATCH * MAX_TPS * 4;
 constexpr int MAX_STAGES = 7;
 constexpr int SMEM_BARS = (3 * MAX_STAGES + 5) * 8;
 constexpr int SMEM_LIMIT = 232448;
-// per epilogue warp: a 32x33 fp32 transpose tile (DW) or a 32-row x 128-byte store staging tile (FWD, DX)
+// per epilogue warp: a 32-row x 128-byte store staging tile (FWD, DX); nothing for the weight gradient
 // `ew`: epilogue warps per TMEM lane quarter and row block (weight gradient of short contractions: 4)
-__host__ __device__ constexpr int smem_epi(int op, int rb, int ew = 1) { return 4 * rb * ew * (op == OP_DW ? SMEM_EPI_WARP : 4096); }
+__host__ __device__ constexpr int smem_epi(int op, int rb, int ew = 1) { return op == OP_DW ? 0 : 4 * rb * ew * 4096; }
 __host__ __device__ constexpr int load_bytes(int ctas, int rb, int nc) { return rb * A_BLOCK_BYTES + (nc / ctas) * 128; }
 __host__ __device__ constexpr int stage_bytes(int ctas, int rb, int split, int nc) { return load_bytes(ctas, rb, nc) * (split ? 2 : 1); }
 __host__ __device__ constexpr int num_stages(int op, int ctas, int rb, int split, int nc, int ew = 1)
@@ -409,7 +410,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
 #pragma unroll
         for (int c2 = 0; c2 < TILE_C / 32; ++c2)
             if (c2 % EW == (int)cgrp) own |= 1u << c2;
-        float *scratch = epi_scratch + (warp - 2) * (OP == OP_DW ? 32 * 33 : 1024);
+        float *scratch = epi_scratch + (warp - 2) * 1024;   // (FWD / DX staging tile; unused by the weight gradient)
         uint32_t tempty_base = bar_tempty;
         if (CTAS == 2) tempty_base = mapa_cluster(bar_tempty, 0);
         uint32_t n_items = 0;
@@ -417,23 +418,23 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
             const uint32_t buf = n_items % NBUF, tph = (n_items / NBUF) & 1;
-            // one lane per warp polls (sleeping in the barrier unit between polls); the others wait for it
-            bool mine = true;
-            if (lane == 0) mine = mbar_wait_bounded(bar_tfull + 8 * buf, tph, RZ_WAIT_TMEM_FULL, p.wait, 20000);
-            ok = __shfl_sync(0xffffffffu, (int)mine, 0) != 0;
-            if (!ok) break;
-            tc_fence_after();
             const uint32_t rbase = tr * ITEM_R + rblk * PAIR_R + rank * TILE_R + q * 32;   // first row of this warp
-            // Weight gradient: the block's eight 32-column chunks of this warp's rows go to slices of the hashed
-            // gradient.  Chunks that land on exactly the same addresses (tiles of one tile row whose offsets
-            // collide, same position inside the tile) are summed in registers first, so a collision costs one
-            // set of reductions instead of one per tile.  Lane c (< 8) holds the destination of chunk c.
-            uint32_t key_off = 0, key_rel = 0, eqmask = 0;
+            // Weight gradient.  The block is computed TRANSPOSED (A = dY, B = X): an accumulator row (TMEM lane) is an
+            // output column n of the virtual weight and an accumulator column is a weight row k.  A thread thus holds,
+            // for its n, 32 consecutive k of a chunk, and the 32 lanes of a warp hold 32 consecutive n - which are 32
+            // consecutive words of one slice row.  Every reduction instruction is therefore one coalesced 128-byte
+            // segment straight out of the registers that tcgen05.ld filled: no transpose through shared memory.
+            // A chunk (32 k) lies inside one hash tile (tiles are multiples of 32 both ways).  Chunks of different
+            // tiles of one tile column that land on exactly the same addresses (colliding offsets, same rows inside the
+            // tile) are summed in registers first, so such a collision costs one set of reductions instead of one
+            // per tile.  Lane c (< chunks per block) holds the destination of chunk c.
+            uint32_t key_off = 0, key_rel = 0, eqmask = 0, n_rel = 0;
             if (OP == OP_DW) {
-                const uint32_t pk = rbase / (uint32_t)p.hash.BK;
+                const uint32_t pn = rbase / (uint32_t)p.hash.BN;
+                n_rel = rbase - pn * (uint32_t)p.hash.BN;
                 if (lane < TILE_C / 32) {
-                    const uint32_t ccol = tc * TILE_C + lane * 32, pn = ccol / (uint32_t)p.hash.BN;
-                    key_rel = ccol - pn * (uint32_t)p.hash.BN;
+                    const uint32_t kcol = tc * TILE_C + lane * 32, pk = kcol / (uint32_t)p.hash.BK;
+                    key_rel = kcol - pk * (uint32_t)p.hash.BK;
                     key_off = (uint32_t)rz_tile_offset(p.hash, pk, pn);
                 }
 #pragma unroll
@@ -442,6 +443,13 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     if (o2 == key_off && r2 == key_rel) eqmask |= 1u << c2;
                 }
             }
+            // (destinations first, then the wait: the hash and the comparisons overlap the block's MMAs)
+            // one lane per warp polls (sleeping in the barrier unit between polls); the others wait for it
+            bool mine = true;
+            if (lane == 0) mine = mbar_wait_bounded(bar_tfull + 8 * buf, tph, RZ_WAIT_TMEM_FULL, p.wait, 20000);
+            ok = __shfl_sync(0xffffffffu, (int)mine, 0) != 0;
+            if (!ok) break;
+            tc_fence_after();
             if (OP == OP_DW && EW > 1) {
                 // Scatter-bound weight gradient.  The warp pulls all its chunks out of TMEM at once and hands the
                 // accumulator back before it starts on the reductions, so the next blocks' MMAs never wait for the
@@ -462,10 +470,8 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     if (CTAS == 2) mbar_arrive_cluster_relaxed(tempty_base + 8 * buf);
                     else mbar_arrive_relaxed(bar_tempty + 8 * buf);
                 }
-                const uint32_t kb = rbase;
-                if (kb >= p.K) continue;
-                const uint32_t nrow = min(32u, p.K - kb);
-                const uint32_t row_in = kb - (kb / (uint32_t)p.hash.BK) * (uint32_t)p.hash.BK;
+                if (rbase >= p.N) continue;
+                const bool lane_ok = rbase + lane < p.N;
                 const uint32_t bn = (uint32_t)p.hash.BN;
 #pragma unroll
                 for (int j = 0; j < NCH; ++j) {
@@ -473,7 +479,8 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     if (c >= TILE_C / 32) break;
                     const uint32_t same = __shfl_sync(0xffffffffu, eqmask, c) & own;
                     if (same & ((1u << c) - 1u)) continue;   // summed into an earlier chunk of this warp
-                    bool col_ok = tc * TILE_C + c * 32 + lane < p.N;
+                    const uint32_t kcol = tc * TILE_C + c * 32;
+                    uint32_t nk = kcol < p.K ? min(32u, p.K - kcol) : 0u;   // weight rows of this chunk that exist
                     float acc[32];
 #pragma unroll
                     for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(vv[j][e]);
@@ -483,29 +490,22 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                         if (c2 < TILE_C / 32 && ((same >> c2) & 1u)) {
 #pragma unroll
                             for (int e = 0; e < 32; ++e) acc[e] += __uint_as_float(vv[j2][e]);
-                            col_ok = col_ok || (tc * TILE_C + c2 * 32 + lane < p.N);
+                            const uint32_t kcol2 = tc * TILE_C + c2 * 32;
+                            nk = max(nk, kcol2 < p.K ? min(32u, p.K - kcol2) : 0u);
                         }
                     }
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) scratch[lane * 33 + e] = acc[e] * p.alpha;
-                    __syncwarp();
                     const uint32_t off = __shfl_sync(0xffffffffu, key_off, c), rel = __shfl_sync(0xffffffffu, key_rel, c);
-                    float *dst = p.dH + off + (uint64_t)row_in * bn + rel + lane;
-                    if (nrow == 32) {
+                    float *dst = p.dH + off + (uint64_t)rel * bn + n_rel + lane;
+                    if (lane_ok) {
+                        if (nk == 32) {
 #pragma unroll
-                        for (int r0 = 0; r0 < 32; r0 += 8) {
-                            float t[8];
+                            for (int e = 0; e < 32; ++e) atomicAdd(dst + (size_t)e * bn, acc[e] * p.alpha);
+                        } else {
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) t[e] = scratch[(r0 + e) * 33 + lane];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                if (col_ok) atomicAdd(dst + (size_t)(r0 + e) * bn, t[e]);
+                            for (int e = 0; e < 32; ++e)
+                                if ((uint32_t)e < nk) atomicAdd(dst + (size_t)e * bn, acc[e] * p.alpha);
                         }
-                    } else {
-                        for (uint32_t rr = 0; rr < nrow; ++rr)
-                            if (col_ok) atomicAdd(dst + (size_t)rr * bn, scratch[rr * 33 + lane]);
                     }
-                    __syncwarp();
                 }
                 continue;
             }
@@ -549,7 +549,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                     float acc[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(v[j]);
-                    bool col_ok = col + lane < p.N;
+                    uint32_t nk = col < p.K ? min(32u, p.K - col) : 0u;   // weight rows of this chunk that exist
                     uint32_t rest = same & ~((2u << c) - 1u);   // later chunks with the same destination
                     while (rest) {
                         const int c2 = __ffs(rest) - 1;
@@ -564,21 +564,17 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
 #pragma unroll
                             for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
                         }
-                        col_ok = col_ok || (tc * TILE_C + c2 * 32 + lane < p.N);
+                        const uint32_t col2 = tc * TILE_C + c2 * 32;
+                        nk = max(nk, col2 < p.K ? min(32u, p.K - col2) : 0u);
                     }
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) scratch[lane * 33 + j] = acc[j] * p.alpha;
-                    __syncwarp();
-                    const uint32_t kb = rbase;
                     const uint32_t off = __shfl_sync(0xffffffffu, key_off, c), rel = __shfl_sync(0xffffffffu, key_rel, c);
-                    if (kb < p.K) {
-                        const uint32_t pk = kb / (uint32_t)p.hash.BK;
-                        float *dst = p.dH + off + (uint64_t)(kb - pk * (uint32_t)p.hash.BK) * (uint32_t)p.hash.BN + rel + lane;
-                        const uint32_t nrow = min(32u, p.K - kb);
-                        for (uint32_t rr = 0; rr < nrow; ++rr)
-                            if (col_ok) atomicAdd(dst + (size_t)rr * (uint32_t)p.hash.BN, scratch[rr * 33 + lane]);
+                    if (rbase + lane < p.N) {
+                        // lane = weight column n, register e = weight row k: one coalesced 128-byte reduction per k
+                        float *dst = p.dH + off + (uint64_t)rel * (uint32_t)p.hash.BN + n_rel + lane;
+#pragma unroll
+                        for (int e = 0; e < 32; ++e)
+                            if ((uint32_t)e < nk) atomicAdd(dst + (size_t)e * (uint32_t)p.hash.BN, acc[e] * p.alpha);
                     }
-                    __syncwarp();
                 } else if (partial) {
                     // split contraction: add the raw fp32 partial sums into this block's ITEM_R x NC workspace tile (a
                     // finalize kernel scales, adds the bias and converts); staged like the store path so every
@@ -1174,16 +1170,17 @@ TcConfig choose_config(const rz_problem *pb, int op)
 {
     const bool bf16 = pb->precision == RZ_PREC_BF16;
     const bool split = pb->precision == RZ_PREC_FP32;
-    const int64_t rows = (op == RZ_OP_BACKWARD_WEIGHT) ? pb->K : pb->M;
-    const int64_t cols = (op == RZ_OP_BACKWARD_INPUT) ? pb->K : pb->N;
+    const int64_t rows = (op == RZ_OP_BACKWARD_WEIGHT) ? pb->N : pb->M;   // (weight gradient: transposed block, N x K)
+    const int64_t cols = (op == RZ_OP_FORWARD) ? pb->N : pb->K;
     const int64_t depth = (op == RZ_OP_FORWARD) ? pb->K : (op == RZ_OP_BACKWARD_INPUT ? pb->N : pb->M);
     const int64_t stages = (depth + (bf16 ? 63 : 31)) / (bf16 ? 64 : 32);
     const int sms = usable_sms(pb);
     auto allowed = [&](const TcConfig &c) {
         if (split && c.rb == 2) return false;                       // split precision has no two-row-block variant
         // with two row blocks the epilogue cannot overlap the next main loop: the contraction must amortise it
-        // (the weight gradient's scatter epilogue is about three times as long as a store epilogue)
-        if (c.rb == 2 && stages < (op == RZ_OP_BACKWARD_WEIGHT ? 32 : 12)) return false;
+        // (the weight gradient's scatter epilogue is several times as long as a store epilogue; measured: at 32 stages
+        // the one-row-block pair with sixteen epilogue warps is 4 % ahead, at 64 stages two row blocks are 6 % ahead)
+        if (c.rb == 2 && stages < (op == RZ_OP_BACKWARD_WEIGHT ? 48 : 12)) return false;
         const int64_t bcols = c.nc / c.ctas;                        // whole B boxes per hash tile (input gradient)
         if (op == RZ_OP_BACKWARD_INPUT && (pb->BK <= bcols ? bcols % pb->BK != 0 : pb->BK % bcols != 0)) return false;
         return true;
@@ -1313,8 +1310,8 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.M = (uint32_t)pb->M;
     p.K = (uint32_t)pb->K;
     p.N = (uint32_t)pb->N;
-    p.rows = (OP == OP_DW) ? p.K : p.M;
-    p.cols = (OP == OP_DX) ? p.K : p.N;
+    p.rows = (OP == OP_DW) ? p.N : p.M;                  // (the weight gradient is computed transposed: N x K)
+    p.cols = (OP == OP_FWD) ? p.N : p.K;
     const uint32_t depth = (OP == OP_FWD) ? p.K : (OP == OP_DX ? p.N : p.M);
     p.tiles_r = (p.rows + ITEM_R - 1) / ITEM_R;
     p.tiles_c = (p.cols + NC - 1) / NC;
@@ -1669,10 +1666,10 @@ int rz_tc_backward_weight(const RzLaunchCtx &c, const void *X, const void *dY, f
     const rz_problem *pb = c.pb;
     const bool tf32 = pb->precision != RZ_PREC_BF16;
     const Geometry g = geometry(pb);
-    CUtensorMap mapA, mapB;
-    int st = map_matrix(&mapA, tf32, true, X, pb->M, pb->K, g.epr, g.epr);
+    CUtensorMap mapA, mapB;   // A = dY (accumulator rows = n), B = X (accumulator columns = k)
+    int st = map_matrix(&mapA, tf32, true, dY, pb->M, pb->N, g.epr, g.epr);
     if (st) return st;
-    st = map_matrix(&mapB, tf32, true, dY, pb->M, pb->N, g.epr, g.epr);
+    st = map_matrix(&mapB, tf32, true, X, pb->M, pb->K, g.epr, g.epr);
     if (st) return st;
     TcParams p;
     memset(&p, 0, sizeof(p));
