@@ -49,8 +49,8 @@ def seeded_R(seed=1005):
 
 # DRAM bytes (read + write) per row of the shard moved by one launch of each tensor-core kernel, from the ncu
 # capture of the 8192-row case of this workload (dram__bytes_read.sum + dram__bytes_write.sum; the traffic
-# grows in proportion to the rows): forward 774 MB, weight gradient 1065 MB, input gradient 817 MB.
-DRAM_BYTES_PER_ROW = {"forward": 776.8e6 / 8192, "backward_weight": 1067.9e6 / 8192, "backward_input": 811.5e6 / 8192}
+# grows in proportion to the rows): forward 779 MB, weight gradient 1071 MB, input gradient 821 MB.
+DRAM_BYTES_PER_ROW = {"forward": 778.8e6 / 8192, "backward_weight": 1070.9e6 / 8192, "backward_input": 821.3e6 / 8192}
 
 
 def measured_peaks():
@@ -269,6 +269,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-cublas", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the module and baseline-configuration measurements")
+    ap.add_argument("--no-long-repeat", action="store_true", help="skip the second, longer timed repeat of short regions")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -377,7 +378,7 @@ def main():
     # A region shorter than half a second runs at boost clocks the power cap would not sustain: a second, longer
     # repeat (about a second and a half) is reported beside it.
     long_repeat = None
-    if ms_step * args.steps < 500.0:
+    if ms_step * args.steps < 500.0 and not args.no_long_repeat:
         n_long = min(2000, int(1500.0 / ms_step) + 1)
         ms_long, clocks_long, _, _ = timed(n_long, False)
         long_repeat = {"steps": n_long, "ms_per_step": ms_long, "value": flops_step / (ms_long * 1e-3) / 1e12,

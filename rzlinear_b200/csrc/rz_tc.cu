@@ -826,10 +826,10 @@ __global__ void rz_sgd_momentum_kernel(float *__restrict__ hashed, const float *
 //   (velocity = momentum * velocity + dH;)   hashed -= lr * (velocity | dH);   copy s, element j = convert(hashed[j + s]).
 // A thread owns one aligned group of NS elements: it updates them in place and writes the NS 16-byte pieces of the
 // shifted copies that start in its group.  Those pieces reach NS - 1 elements into the NEXT group, whose new values
-// come from the neighbouring lane (shuffle) or warp (shared memory) of the same 256-group chunk.  The last group of
+// come from the neighbouring lane (shuffle) or warp (shared memory) of the same chunk of SGD_CHUNK groups.  The last group of
 // a chunk has its neighbour in another block, which may or may not have updated it yet: its pieces for copies
 // 1 .. NS-1 are left to the block that finishes last (a ticket counter tells which), which by then reads final values.
-constexpr int SGD_CHUNK = 256;     // groups per block iteration (= threads per block)
+constexpr int SGD_CHUNK = 1024;    // groups per block iteration (= threads per block): few chunk boundaries for the last block
 constexpr int SGD_TICKETS = 64;    // launches that may be in flight at once, one ticket word each
 __device__ unsigned g_sgd_ticket[SGD_TICKETS];
 
@@ -1600,7 +1600,7 @@ int rz_tc_sgd_step(const RzLaunchCtx &c, float *hashed, const float *dH, float *
     const Geometry g = geometry(c.pb);
     const uint32_t groups = g.Hc / g.ns;
     uint32_t blocks = (groups + SGD_CHUNK - 1) / SGD_CHUNK;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > 148 * 2) blocks = 148 * 2;
     const bool tf32 = c.pb->precision != RZ_PREC_BF16;
     const int raw = c.pb->precision == RZ_PREC_FP32 ? 1 : 0;
     uint8_t *sh = static_cast<uint8_t *>(shadow);

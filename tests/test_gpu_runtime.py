@@ -18,7 +18,7 @@ def _problem(rzlib, M, K, N, H, BK, BN, prec, **kw):
 
 
 @pytest.mark.parametrize("prec_name", ["bf16", "tf32", "fp32"])
-@pytest.mark.parametrize("H", [1 << 17, 100003, 64 * 64 + 1, 2055, 3 * 256 * 8 + 5])   # (2055: one word more than a 32 x 64 tile)
+@pytest.mark.parametrize("H", [1 << 17, 100003, 64 * 64 + 1, 2055, 3 * 1024 * 8 + 5])   # (2055: one word more than a 32 x 64 tile)
 @pytest.mark.parametrize("momentum", [0.0, 0.9])
 def test_optimiser_step_rewrites_the_shadow_in_the_same_launch(rzlib, prec_name, H, momentum):
     # hashed / velocity against fp64 arithmetic; the shadow bit-identical to a refresh from the updated array
