@@ -269,6 +269,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-cublas", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the module and baseline-configuration measurements")
+    ap.add_argument("--comm-sms", type=int, default=None, help="SMs the input gradient leaves to the all-reduce (N > 1)")
     ap.add_argument("--no-long-repeat", action="store_true", help="skip the second, longer timed repeat of short regions")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -301,7 +302,8 @@ def main():
     lo, hi = shard_rows(m_global, rank, world)
     M = hi - lo
     R = seeded_R()
-    step = RzDataParallelStep(M, K, N, H, BK, BN, R, _lib.HASH_SINGLE, torch.bfloat16, LR, dev)
+    extra = {} if args.comm_sms is None else {"comm_sms": args.comm_sms}
+    step = RzDataParallelStep(M, K, N, H, BK, BN, R, _lib.HASH_SINGLE, torch.bfloat16, LR, dev, **extra)
     assert _lib.plan(step.pb, 0) == _lib.PATH_TCGEN05
 
     # synthetic shard, generated on the device in slabs (seeded per rank), resident before timing starts

@@ -21,11 +21,7 @@ class RzLinear(torch.nn.Module):
     R = 8
     LARGE_PRIME = 2038074743
 
-    '''
-        Args:
-            P (int): The prime number used in the hash function
-            R (int): Number of random numbers
-    '''
+    # P: default prime of the tile hash.  R: how many random numbers a layer carries (R[0] is the prime itself).
 
     def __init__(self, input_dim: int, output_dim: int, chunk_size: int = 1,
                  hashed_weight: Parameter = None, tiled=True, seed: int = 1024, bias: bool = True,
@@ -35,25 +31,32 @@ class RzLinear(torch.nn.Module):
                  prime: Optional[int] = None, random_numbers: Optional[Sequence[int]] = None,
                  relu: bool = False) -> None:
         '''
-            A Linear layer using ROBE-Z compression
+            Linear layer whose input_dim x output_dim weight is virtual: every block_size_k x block_size_n tile of it
+            is a contiguous slice of one shared 1-D parameter, `hashed_weight`, at an offset given by a hash of the
+            tile's coordinates (ROBE-Z).
 
-            Args:
-                input_dim (int): Number of features in each input sample
-                output_dim (int): Number of features in each output sample
-                compress_ratio (float): size of hashed_weight relative to (input_dim, output_dim)
-                chunk_size (int): The size of the minimal hash unit. Unused, as in the reference
-                hashed_weight (Tensor): if given, it is reused (shared between layers) and compress_ratio ignored
-                seed (int): The random seed to init random numbers
-                bias (bool): If True, adds a learnable bias to the output
-                dtype (float): The default data type of parameters
-                block_size_k, block_size_n (int): the hash tile; part of the definition of the virtual
-                    matrix (the reference's kernels default to 32 x 64)
-                hash_mode (str): 'two_level' (what the reference's kernels execute) or 'single'
-                    (((pk*R3 + pn*R2 + R1) mod P) mod (H - BK*BN))
-                prime (int): overrides RzLinear.P for this layer
-                random_numbers (sequence of 8 ints): overrides the seeded random numbers; [0] is the prime
-                relu (bool): apply ReLU inside the forward kernel
+            Positional arguments, same order and meaning as the reference's constructor:
+                input_dim, output_dim (int): feature counts of the input and of the output (both below 10^5)
+                chunk_size (int): kept for call compatibility; neither implementation uses it
+                hashed_weight (Parameter): an existing compressed array to share with other layers; when given,
+                    compress_ratio plays no part
+                tiled (bool): kept for call compatibility, unused
+                seed (int): seeds the draw of the layer's random numbers
+                bias (bool): whether the layer owns a bias vector of output_dim entries
+                dtype (torch.dtype): dtype of the parameters this layer creates
+                compress_ratio (float): length of a newly created hashed_weight as a fraction of input_dim * output_dim
+                init_factor (float): constant the product is multiplied by
+
+            Keyword-only additions:
+                block_size_k, block_size_n (int): the hash tile. It is part of what defines the virtual matrix; the
+                    reference's kernels use 32 x 64 unless told otherwise
+                hash_mode (str): 'two_level', the form the reference's kernels evaluate, or 'single',
+                    ((pk*R3 + pn*R2 + R1) mod P) mod (H - BK*BN)
+                prime (int): this layer's prime instead of RzLinear.P
+                random_numbers (8 ints): use these instead of drawing from the seed; entry 0 is the prime
+                relu (bool): fuse a ReLU into the forward kernel's epilogue
         '''
+
         super(RzLinear, self).__init__()
 
         assert (input_dim < 10**5 and output_dim < 10**5)
@@ -110,13 +113,8 @@ class RzLinear(torch.nn.Module):
 
     def forward(self, x) -> torch.Tensor:
         '''
-            RzLinear forward function, which computes rzlinear and bias (if any)
-
-            Args:
-                input (Tensor): (N, *, input_dim), where N is the batch size
-
-            Returns:
-                output (Tensor): (N, *, output_dim)
+            x: (batch, ..., input_dim) -> (batch, ..., output_dim).  Leading dimensions are flattened for the kernel
+            and restored afterwards; the bias (if any) and the optional ReLU are applied inside the kernel.
         '''
         assert (len(x.shape) >= 2)
         dim_gt_2 = x.dim() > 2

@@ -94,6 +94,7 @@ class RzDataParallelStep:
         self.Y = torch.empty((M_local, N), dtype=dtype, device=self.device)
         self.dX = torch.empty((M_local, K), dtype=dtype, device=self.device)
         self._pipe = None
+        self._comm_stream = None
 
     def load_weights(self, hashed: torch.Tensor) -> None:
         self.hashed.copy_(hashed.to(self.hashed.dtype), non_blocking=True)
@@ -116,16 +117,35 @@ class RzDataParallelStep:
         mark("forward")
         k.backward_weight(X, dY, self.dH)
         mark("backward_weight")
+        # The input gradient is queued BEFORE the collective, and the collective is issued from a side stream that
+        # waits for the weight gradient only: when the weight gradient finishes, the persistent input-gradient CTAs
+        # are placed first (on all SMs but `comm_sms`) and the collective's CTAs take the SMs left idle.  Issued
+        # the other way round, the collective's CTAs land first, anywhere, and the input-gradient CTAs they displace
+        # start only when it is over - with a static work split that delays the whole kernel by the collective's time.
         work = None
-        if self.world > 1:
+        on_gpu = self.device.type == "cuda"
+        if self.world > 1 and on_gpu:
+            dh_ready = torch.cuda.Event()
+            dh_ready.record()
+        elif self.world > 1:   # host-logic tests on CPU (gloo): no streams to order
             work = dist.all_reduce(self.dH, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
         k.backward_input(dY, self.hashed, self.dX)
+        if self.world > 1 and on_gpu:
+            work = self._all_reduce_beside(dh_ready)
         mark("backward_input")
         if work is not None:
             work.wait()
         mark("comm_wait")   # what of the all-reduce was still running when the input gradient had finished
         self._update()
         mark("sgd")
+
+    def _all_reduce_beside(self, dh_ready):
+        """Start the all-reduce of dH on the communication stream, ordered after `dh_ready` only."""
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=self.device)
+        self._comm_stream.wait_event(dh_ready)
+        with torch.cuda.stream(self._comm_stream):
+            return dist.all_reduce(self.dH, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
 
     def _host_pipeline(self, chunk_rows: int):
         """Device staging buffers, the copy stream, per-chunk problems and events of step_host."""
@@ -184,8 +204,11 @@ class RzDataParallelStep:
             _lib.forward(pb, x, self.hashed, shadow, None, self.Y[lo:hi])
             _lib.backward_weight(pb, x, dy, self.dH)
             if i == last and self.world > 1:
-                work = dist.all_reduce(self.dH, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+                dh_ready = torch.cuda.Event()
+                dh_ready.record()
             _lib.backward_input(pb_dx, dy, self.hashed, shadow, self.dX[lo:hi])
+            if i == last and self.world > 1:
+                work = self._all_reduce_beside(dh_ready)
             ev = torch.cuda.Event()
             ev.record(main)
             pipe["consumed"][i] = ev
