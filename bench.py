@@ -295,6 +295,10 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # The all-reduce of the hashed gradient runs beside the persistent input-gradient kernel, on the SMs that
+        # kernel leaves idle (RzDataParallelStep's comm_sms, 8 by default): NCCL must not ask for more CTAs than fit
+        # there, or the rest of its CTAs wait for the input gradient to end (measured: nothing hidden then).
+        os.environ.setdefault("NCCL_MAX_CTAS", str(8 if args.comm_sms is None else max(1, args.comm_sms)))
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
 

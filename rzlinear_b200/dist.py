@@ -6,7 +6,9 @@ hashed-weight gradient over ranks (one all-reduce of H floats), launched right a
 weight-gradient kernel so that it overlaps the input-gradient kernel; every rank then applies the
 same SGD update, so the replicas stay identical.  The input-gradient kernel is persistent (one CTA
 per SM), so with more than one rank it is launched on all SMs but `comm_sms`: the collective's
-CTAs get those and run beside it instead of behind it.
+CTAs get those and run beside it instead of behind it.  For that the collective must fit those SMs: create the
+NCCL process group with at most `comm_sms` CTAs (environment `NCCL_MAX_CTAS`, or the process-group option
+`config.max_ctas`); with NCCL's default CTA count part of the collective still waits for the input gradient to end.
 
 The reference has no distributed code; this follows its single-GPU step
 (python/rz_linear/RzLinearFunction.py:14-60) per rank.
