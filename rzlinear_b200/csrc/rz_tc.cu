@@ -91,6 +91,7 @@ struct TcParams {
     uint32_t nsplit, chunks_per_split;   // blocks from index n_main on are split into nsplit parts of the contraction
     uint32_t n_main;                      // blocks [0, n_main) run their whole contraction in one work item
     uint32_t total_items;
+    uint32_t units;             // > 0: the launch's (block, stage) units are dealt out in equal ranges (tiles * nchunks)
     uint32_t br;                // slice rows per B box (FWD: min(BK, stage depth); DX: min(BK, B columns of this CTA))
     uint32_t kparts;            // FWD: B boxes along the contraction per 128-byte column block (stage depth / br)
     uint32_t group_rows;        // row tiles per rasterisation group
@@ -211,20 +212,43 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
 
     bool ok = true;
 
-    // decode a work item into its output block and contraction range; `tile` is the block index in rasterisation
-    // order, `partial` says that the item is one of several parts of its block's contraction
-    uint32_t tile = 0;
+    // Work of this CTA (pair).  Two schedules:
+    //  * items: work item i = one block with its whole contraction, or one of the nsplit parts of a split block; the
+    //    CTA takes items first_item, first_item + item_stride, ...
+    //  * units (p.units > 0, small grids whose every block is split): the (block, stage) pairs of the whole launch,
+    //    block-major, are dealt out in equal contiguous ranges, one per CTA, so every SM gets the same number of
+    //    stages whatever the number of blocks; a range that crosses a block boundary is worked off as two segments.
+    // `item` below is the cursor of either schedule; decode() turns it into a block and a stage range and sets the
+    // next cursor.  `tile` is the block index in rasterisation order, `partial` says that the segment is only a part
+    // of its block's contraction (its result goes to the workspace as fp32 partial sums).
+    uint32_t cur_begin = first_item, cur_end = p.total_items;
+    if (p.units) {
+        cur_begin = (uint32_t)(((uint64_t)first_item * p.units) / item_stride);
+        cur_end = (uint32_t)(((uint64_t)(first_item + 1) * p.units) / item_stride);
+    }
+    uint32_t tile = 0, next_item = 0;
     bool partial = false;
     auto decode = [&](uint32_t item, uint32_t &tr, uint32_t &tc, uint32_t &c_begin, uint32_t &c_end) {
-        uint32_t split = 0;
-        if (item < p.n_main) {
-            tile = item;
-            partial = false;
+        if (p.units) {
+            tile = item / p.nchunks;
+            c_begin = item - tile * p.nchunks;
+            c_end = min(p.nchunks, c_begin + (cur_end - item));
+            partial = true;
+            next_item = item + (c_end - c_begin);
         } else {
-            const uint32_t idx = item - p.n_main, q = idx / p.nsplit;
-            tile = p.n_main + q;
-            split = idx - q * p.nsplit;
-            partial = p.nsplit > 1;
+            uint32_t split = 0;
+            if (item < p.n_main) {
+                tile = item;
+                partial = false;
+            } else {
+                const uint32_t idx = item - p.n_main, q = idx / p.nsplit;
+                tile = p.n_main + q;
+                split = idx - q * p.nsplit;
+                partial = p.nsplit > 1;
+            }
+            c_begin = partial ? split * p.chunks_per_split : 0u;
+            c_end = partial ? min(p.nchunks, c_begin + p.chunks_per_split) : p.nchunks;
+            next_item = item + item_stride;
         }
         uint32_t per_group = p.group_rows * p.tiles_c;
         uint32_t group = tile / per_group, within = tile - group * per_group;
@@ -232,8 +256,6 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         uint32_t gsz = min(p.tiles_r - first_r, p.group_rows);
         tr = first_r + within % gsz;
         tc = within / gsz;
-        c_begin = partial ? split * p.chunks_per_split : 0u;
-        c_end = partial ? min(p.nchunks, c_begin + p.chunks_per_split) : p.nchunks;
     };
 
     if (warp == 0) {
@@ -242,7 +264,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         // transaction bytes of a stage are counted on the leader's barrier
         uint32_t full_base = bar_full;
         if (PAIR_LOADS) full_base = mapa_cluster(bar_full, 0);
-        for (uint32_t item = first_item; item < p.total_items && ok; item += item_stride) {
+        for (uint32_t item = cur_begin; item < cur_end && ok; item = next_item) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
             const uint32_t row0 = tr * ITEM_R + rank * TILE_R;     // first output row staged by this CTA (A); row block r adds r * PAIR_R
@@ -342,7 +364,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     } else if (warp == 1) {
         // ===================== MMA issuer (leader CTA only) =====================
         uint32_t it = 0, n_items = 0;
-        for (uint32_t item = first_item; item < p.total_items && ok && rank == 0; item += item_stride, ++n_items) {
+        for (uint32_t item = cur_begin; item < cur_end && ok && rank == 0; item = next_item, ++n_items) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
             const uint32_t buf = n_items % NBUF, tph = (n_items / NBUF) & 1;
@@ -414,7 +436,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         uint32_t tempty_base = bar_tempty;
         if (CTAS == 2) tempty_base = mapa_cluster(bar_tempty, 0);
         uint32_t n_items = 0;
-        for (uint32_t item = first_item; item < p.total_items && ok; item += item_stride, ++n_items) {
+        for (uint32_t item = cur_begin; item < cur_end && ok; item = next_item, ++n_items) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
             const uint32_t buf = n_items % NBUF, tph = (n_items / NBUF) & 1;
@@ -690,7 +712,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
         uint32_t split_base = bar_split;
         if (CTAS == 2) split_base = mapa_cluster(bar_split, 0);
         uint32_t it = 0;
-        for (uint32_t item = first_item; item < p.total_items && ok; item += item_stride) {
+        for (uint32_t item = cur_begin; item < cur_end && ok; item = next_item) {
             uint32_t tr, tc, c_begin, c_end;
             decode(item, tr, tc, c_begin, c_end);
             for (uint32_t c = c_begin; c < c_end && ok; ++c, ++it) {
@@ -1120,9 +1142,10 @@ uint32_t env_u32(const char *name, uint32_t dflt)
 // Bring-up / A-B knobs, read from the environment once (rz_reload_env() reads them again):
 //   RZ_TC_CONFIG 1..5 forces a block shape, RZ_TC_NOSPLIT=1 turns contraction splitting off, RZ_TC_EW_STAGES is the
 //   longest contraction (stages) that gets the sixteen-warp weight-gradient epilogue, RZ_TC_GROUP the rasterisation
-//   group (row tiles), RZ_TC_TMA_STORE=0 plain stores instead of bulk tensor stores, RZ_TC_VERBOSE=1 one line per launch.
+//   group (row tiles), RZ_TC_TMA_STORE=0 plain stores instead of bulk tensor stores, RZ_TC_VERBOSE=1 one line per launch,
+//   RZ_TC_UNIT_RANGES=0 keeps fully split launches on nsplit equal parts per block instead of equal stage ranges.
 struct Knobs {
-    std::atomic<uint32_t> config{0}, no_split{0}, ew_stages{64}, group{0}, tma_store{1}, verbose{0};
+    std::atomic<uint32_t> config{0}, no_split{0}, ew_stages{64}, group{0}, tma_store{1}, verbose{0}, unit_ranges{1};
     std::atomic<bool> ready{false};
 };
 Knobs g_knobs;
@@ -1135,6 +1158,7 @@ void load_knobs()
     g_knobs.group.store(env_u32("RZ_TC_GROUP", 0));
     g_knobs.tma_store.store(env_u32("RZ_TC_TMA_STORE", 1));
     g_knobs.verbose.store(env_u32("RZ_TC_VERBOSE", 0));
+    g_knobs.unit_ranges.store(env_u32("RZ_TC_UNIT_RANGES", 1));
     g_knobs.ready.store(true, std::memory_order_release);
 }
 
@@ -1410,10 +1434,23 @@ int launch_tc(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorMap &
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (a_major << 15) | (b_major << 16) | ((uint32_t)(NC >> 3) << 17) |
               ((uint32_t)(PAIR_R >> 4) << 24);
 
+    uint32_t blocks = p.total_items < (uint32_t)slots ? p.total_items : (uint32_t)slots;
+    // Small grids whose every block is split anyway (FWD / DX): deal the (block, stage) units out in equal ranges
+    // instead of nsplit equal parts per block, so that every SM works whatever the number of blocks (40 blocks in
+    // 3 parts keep 120 of 148 SMs busy; 148 ranges keep them all).  Not for split precision, whose parts also
+    // bound the accumulation chains.
+    p.units = 0;
+    if (OP != OP_DW && !SPLIT && p.nsplit > 1 && p.n_main == 0 && knobs().unit_ranges.load(std::memory_order_relaxed)) {
+        const uint32_t units = tiles * p.nchunks;
+        uint32_t ranges = units / 8 < (uint32_t)slots ? units / 8 : (uint32_t)slots;   // at least 8 stages per range
+        if (ranges > blocks) {
+            p.units = units;
+            blocks = ranges;
+        }
+    }
     if (knobs().verbose.load(std::memory_order_relaxed))   // bring-up aid: one line per launch on stderr
-        fprintf(stderr, "rz_tc op %d tf32 %d block (%d,%d,%d) ew %d stages %d: %u blocks, %u whole + %u x %u parts, %d slots\n", OP,
-                (int)TF32, CTAS, RB, NC, EW, STAGES_HOST, tiles, p.n_main, tiles - p.n_main, p.nsplit, slots);
-    const uint32_t blocks = p.total_items < (uint32_t)slots ? p.total_items : (uint32_t)slots;
+        fprintf(stderr, "rz_tc op %d tf32 %d block (%d,%d,%d) ew %d stages %d: %u blocks, %u whole + %u x %u parts, %d slots, %u units in %u ranges\n", OP,
+                (int)TF32, CTAS, RB, NC, EW, STAGES_HOST, tiles, p.n_main, tiles - p.n_main, p.nsplit, slots, p.units, p.units ? blocks : 0u);
     cfg.gridDim = dim3(blocks * CTAS, 1, 1);
     const bool partial = OP != OP_DW && p.nsplit > 1;
     const uint32_t split_tiles = tiles - p.n_main;
