@@ -154,6 +154,14 @@ class RzDataParallelStep:
         if getattr(self, "_pipe", None) is not None and self._pipe["chunk_rows"] == chunk_rows:
             return self._pipe
         spans = [(lo, min(self.M, lo + chunk_rows)) for lo in range(0, self.M, chunk_rows)]
+        # What follows the last copy cannot overlap anything: the kernels of the last chunk, the update, the read-back.
+        # So the last chunk is cut into halves of halves (down to 2048 rows): the copies stay large, the tail short.
+        lo, hi = spans.pop()
+        while hi - lo >= 2 * 2048:
+            mid = lo + (hi - lo) // 2 // 128 * 128
+            spans.append((lo, mid))
+            lo = mid
+        spans.append((lo, hi))
         base = self.pb
         problems = []
         for i, (lo, hi) in enumerate(spans):
