@@ -228,6 +228,37 @@ def test_module_matches_reference_fixture(golden_dir):
     assert o.rel_l2(rz._bias.grad.cpu().numpy(), d["dbias"]) < TOL_FP32
 
 
+def test_default_module_on_bf16_activations_runs_the_tensor_core_path(rzlib):
+    # RzLinear with nothing but its dimensions: the reference's defaults (two-level hash, prime 45007, 32 x 64 hash
+    # tile, compress_ratio 1/16).  On bf16 activations all three products take the tcgen05 kernels.
+    from rzlinear_b200 import RzLinear
+    torch.manual_seed(11)
+    K, N, M = 512, 768, 320
+    rz = RzLinear(K, N, seed=7).to(DEV)
+    H = rz._hashed_weight.numel()
+    with torch.no_grad():
+        rz._hashed_weight.copy_((torch.rand(H, device=DEV) * 2 - 1) / K ** 0.5)
+        rz._bias.copy_(torch.randn(N, device=DEV) * 0.1)
+    R = [int(v) for v in rz._random_numbers]
+    pb = rzlib.make_problem(M, K, N, H, 32, 64, R, rzlib.HASH_TWO_LEVEL, rzlib.BF16, rzlib.PREC_BF16)
+    assert all(rzlib.plan(pb, op) == rzlib.PATH_TCGEN05 for op in (0, 1, 2))
+    x = torch.randn(M, K, device=DEV).bfloat16().requires_grad_(True)
+    gy = torch.randn(M, N, device=DEV).bfloat16()
+    n0 = rzlib.launch_count()
+    y = rz(x)
+    y.backward(gy)
+    torch.cuda.synchronize()
+    check_status(rzlib)
+    assert rzlib.launch_count() - n0 <= 8            # refresh, forward, bias-gradient pass, dX, memset-free dH ...
+    hf = o.bf16_round(rz._hashed_weight.detach().cpu().numpy())
+    xf, gf = x.detach().float().cpu().numpy(), gy.float().cpu().numpy()
+    want_y = o.forward(xf, hf, N, 32, 64, R, 1) + rz._bias.detach().cpu().numpy().astype(np.float64)
+    assert o.rel_l2(y.detach().float().cpu().numpy(), want_y) < TOL_TC
+    assert o.rel_l2(x.grad.float().cpu().numpy(), o.backward_input(gf, hf, K, 32, 64, R, 1)) < TOL_TC
+    assert o.rel_l2(rz._hashed_weight.grad.cpu().numpy(), o.backward_weight(xf, gf, H, 32, 64, R, 1)) < TOL_TC
+    assert o.rel_l2(rz._bias.grad.cpu().numpy(), gf.sum(0)) < 1e-5
+
+
 def test_module_accepts_float16_activations():
     # float16 is not a kernel dtype: the layer computes in float32 (tf32 allowed by default) and casts back
     from rzlinear_b200 import RzLinear
