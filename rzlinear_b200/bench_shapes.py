@@ -46,7 +46,22 @@ BASELINE = [("fp32", 1024, 1024, 1024, 65536, 32, 32),
             ("bf16", 8192, 8192, 32768, 1 << 22, 128, 128)]
 
 
-def measure(precision: str, M: int, K: int, N: int, H: int, block_k: int, block_n: int, reps: int, device="cuda:0") -> dict:
+def _time_graph(fn, reps):
+    """fn captured once in a CUDA graph, then replayed: the figure without per-launch host time."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()                      # first-use set-up happens outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return _time(g.replay, reps)
+
+
+def measure(precision: str, M: int, K: int, N: int, H: int, block_k: int, block_n: int, reps: int, device="cuda:0",
+            graph: bool = False) -> dict:
     """forward / hashed-weight gradient / input gradient of one shape through the C ABI, and torch.matmul on a dense
     weight of the same shape (the reference's comparison line, python/bench/bench.py:40-42,78-79,120-121)."""
     dev = torch.device(device)
@@ -78,6 +93,23 @@ def measure(precision: str, M: int, K: int, N: int, H: int, block_k: int, block_
             "cublas_backward_weight": _time(lambda: torch.matmul(X.t(), dY, out=dW), reps),
             "cublas_backward_input": _time(lambda: torch.matmul(dY, W.t(), out=dX), reps),
         }
+        graphed = None
+        if graph:   # launch-bound problems: the three products back to back as one CUDA graph, ours and cuBLAS
+            def ours_all():
+                _lib.forward(pb, X, h, shadow, None, Y)
+                _lib.backward_weight(pb, X, dY, dH)
+                _lib.backward_input(pb, dY, h, shadow, dX)
+
+            def dense_all():
+                torch.matmul(X, W, out=Y)
+                torch.matmul(X.t(), dY, out=dW)
+                torch.matmul(dY, W.t(), out=dX)
+
+            g_ours, g_dense = _time_graph(ours_all, 5 * reps), _time_graph(dense_all, 5 * reps)
+            graphed = {"fwd_bwd_tflops": round(6.0 * M * N * K * 1e-12 / (g_ours * 1e-3), 2),
+                       "cublas_fwd_bwd_tflops": round(6.0 * M * N * K * 1e-12 / (g_dense * 1e-3), 2),
+                       "pct_of_cublas": round(100.0 * g_dense / g_ours, 1),
+                       "what": "forward + weight gradient + input gradient captured in one CUDA graph and replayed"}
     finally:
         torch.backends.cuda.matmul.allow_tf32 = was_tf32
     tflops = {k: 2.0 * M * N * K * 1e-12 / (v * 1e-3) for k, v in ms.items()}
@@ -87,7 +119,7 @@ def measure(precision: str, M: int, K: int, N: int, H: int, block_k: int, block_
             "path": "tcgen05" if _lib.plan(pb, 0) == _lib.PATH_TCGEN05 else "fma",
             "tflops": {k: round(v, 2) for k, v in tflops.items()},
             "fwd_bwd_tflops": round(6.0 * M * N * K * 1e-12 / (ours * 1e-3), 2),
-            "pct_of_cublas": round(100.0 * dense / ours, 1)}
+            "pct_of_cublas": round(100.0 * dense / ours, 1), **({"cuda_graph": graphed} if graphed else {})}
 
 
 def run(precision: str, reps: int, block_k: int = 32, block_n: int = 64, device="cuda:0", shapes=None, hashed=None):

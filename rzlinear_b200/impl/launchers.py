@@ -74,7 +74,10 @@ def cached_shadow(pb, hashed_weight: torch.Tensor, hashed_f32: torch.Tensor) -> 
     (optimisers, copy_, add_) bump the counter; writes through `.data` or from foreign code do not, exactly
     as for autograd's own saved-tensor check: call `drop_shadow_cache(hashed_weight)` after such a write.
     A forward on unchanged weights (evaluation, several layers sharing one hashed array, several
-    micro-batches per optimiser step) therefore allocates nothing and launches no refresh."""
+    micro-batches per optimiser step) therefore allocates nothing and launches no refresh.
+    While a CUDA graph is being captured the refresh is always launched (it becomes a node of the graph): a replay
+    runs none of this Python, so a graph that skipped the refresh would keep reading the shadow of the weights it
+    was captured with."""
     _lib._require_cuda(hashed_f32)
     nbytes = _lib.shadow_bytes(pb)
     if nbytes == 0:
@@ -89,6 +92,11 @@ def cached_shadow(pb, hashed_weight: torch.Tensor, hashed_f32: torch.Tensor) -> 
     key = (pb.H, pb.BK, pb.BN, pb.precision)
     version, ptr = hashed_weight._version, hashed_weight.data_ptr()
     stream = torch.cuda.current_stream(hashed_f32.device)
+    if torch.cuda.is_current_stream_capturing():
+        # a buffer from the graph's own memory pool, filled by a node of the graph; the eager cache is left alone
+        shadow = torch.empty(nbytes, dtype=torch.uint8, device=hashed_f32.device)
+        _lib.shadow_refresh(pb, hashed_f32, shadow)
+        return shadow
     entry = cache.get(key)
     if entry is not None and entry["shadow"].numel() >= nbytes and entry["shadow"].device == hashed_f32.device:
         if entry["version"] == version and entry["ptr"] == ptr:

@@ -177,3 +177,53 @@ def test_launches_are_refused_after_a_wait_gave_up_until_acknowledged(rzlib):
     rzlib.forward(pb, X, h, shadow, None, Y)                   # acknowledged: back to normal
     torch.cuda.synchronize()
     assert torch.equal(Y, good) and rzlib.device_status() == (0, 0)
+
+
+def test_training_step_replayed_from_a_cuda_graph(rzlib):
+    # forward, backward and an in-place SGD update of a small layer captured once and replayed: every replay must see
+    # the weights the previous one wrote (the shadow refresh has to be a node of the graph, not a cached buffer)
+    from rzlinear_b200 import RzLinear
+    torch.manual_seed(2)
+    K, N, M, lr = 256, 512, 256, 0.05
+
+    def make():
+        hw = torch.nn.Parameter(((torch.rand(1 << 16, generator=torch.Generator().manual_seed(3)) * 2 - 1) / 16).to(DEV))
+        return RzLinear(K, N, hashed_weight=hw, seed=5, bias=False, block_size_k=64, block_size_n=64).to(DEV), hw
+
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    t = torch.randn(M, N, device=DEV).bfloat16()
+
+    def step(layer, hw):
+        hw.grad = None
+        loss = (layer(x).float() - t.float()).square().mean()
+        loss.backward()
+        with torch.no_grad():
+            hw.add_(hw.grad, alpha=-lr)
+        return loss
+
+    eager, hw_e = make()
+    losses_e = [float(step(eager, hw_e)) for _ in range(4)]
+
+    graphed, hw_g = make()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):          # warm-up outside the capture: first-use set-up of the library, autograd
+        step(graphed, hw_g)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.no_grad():
+        hw_g.copy_(make()[1])              # back to the initial weights
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        loss_g = step(graphed, hw_g)
+    losses_g = []
+    with torch.no_grad():
+        hw_g.copy_(make()[1])
+    for _ in range(4):
+        g.replay()
+        losses_g.append(float(loss_g))
+    torch.cuda.synchronize()
+    assert rzlib.device_status() == (0, 0)
+    assert losses_e[0] > losses_e[-1]                                   # it trains
+    for a, b in zip(losses_e, losses_g):
+        assert abs(a - b) < 2e-3 * abs(a), (losses_e, losses_g)
+    assert o.rel_l2(hw_g.detach().cpu().numpy(), hw_e.detach().cpu().numpy()) < 1e-4
