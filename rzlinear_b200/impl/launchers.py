@@ -90,7 +90,10 @@ def cached_shadow(pb, hashed_weight: torch.Tensor, hashed_f32: torch.Tensor) -> 
         except AttributeError:      # a tensor subclass without a __dict__: no caching
             return alloc_shadow(pb, hashed_f32)
     key = (pb.H, pb.BK, pb.BN, pb.precision)
-    version, ptr = hashed_weight._version, hashed_weight.data_ptr()
+    try:
+        version, ptr = hashed_weight._version, hashed_weight.data_ptr()
+    except RuntimeError:            # inference tensors keep no version counter: nothing to key a cache on
+        return alloc_shadow(pb, hashed_f32)
     stream = torch.cuda.current_stream(hashed_f32.device)
     if torch.cuda.is_current_stream_capturing():
         # a buffer from the graph's own memory pool, filled by a node of the graph; the eager cache is left alone
