@@ -135,7 +135,8 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     constexpr int STAGES = num_stages(OP, CTAS, RB, SPLIT, NC, EW);
     constexpr bool PAIR_LOADS = (CTAS == 2) && !SPLIT;            // loads of both CTAs counted on the leader's barrier
     constexpr int EPI_WARPS = 4 * RB * EW;
-    static_assert(EW == 1 || (OP == OP_DW && RB == 1 && !SPLIT), "extra epilogue warps: weight gradient, one row block");
+    static_assert(EW == 1 || (OP == OP_DW && !SPLIT && ((RB == 1 && EW == 4) || (RB == 2 && EW == 2))),
+                  "extra epilogue warps: weight gradient only (sixteen warps either way)");
     static_assert(!SPLIT || (TF32 && RB == 1), "split precision: fp32 operands, one row block");
     constexpr int SMEM_RING = STAGES * STAGE_BYTES;
     constexpr int SMEM_EPI_OP = smem_epi(OP, RB, EW);
@@ -426,8 +427,8 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
     } else if (warp < 2 + EPI_WARPS) {
         // ===================== epilogue (both CTAs; each drains its own 128 rows) =====================
         const uint32_t q = warp & 3;          // TMEM lane quarter this warp may read
-        const uint32_t rblk = EW > 1 ? 0u : (warp - 2) >> 2;  // which accumulator (row block) of the item this warp drains
-        const uint32_t cgrp = EW > 1 ? (warp - 2) >> 2 : 0u;  // EW > 1: this warp takes the 32-column chunks cgrp, cgrp + EW, ...
+        const uint32_t rblk = ((warp - 2) >> 2) % RB;   // which accumulator (row block) of the item this warp drains
+        const uint32_t cgrp = ((warp - 2) >> 2) / RB;   // EW > 1: this warp takes the 32-column chunks cgrp, cgrp + EW, ...
         uint32_t own = 0;                                     // mask of those chunks
 #pragma unroll
         for (int c2 = 0; c2 < TILE_C / 32; ++c2)
@@ -472,7 +473,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
             ok = __shfl_sync(0xffffffffu, (int)mine, 0) != 0;
             if (!ok) break;
             tc_fence_after();
-            if (OP == OP_DW && EW > 1) {
+            if (OP == OP_DW && EW > 1 && RB == 1) {
                 // Scatter-bound weight gradient.  The warp pulls all its chunks out of TMEM at once and hands the
                 // accumulator back before it starts on the reductions, so the next blocks' MMAs never wait for the
                 // scatter; loads from TMEM then come in one short burst per block instead of trickling in between
@@ -531,7 +532,7 @@ rz_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ C
                 }
                 continue;
             }
-#pragma nv_diag_suppress 128   // (the EW > 1 instantiations never reach the generic chunk loop)
+#pragma nv_diag_suppress 128   // (the one-row-block EW > 1 instantiations never reach the generic chunk loop)
             // FWD / DX: the next chunk streams out of TMEM while this one is converted and stored
             constexpr bool PREFETCH = (OP != OP_DW) && !SPLIT;
             const uint32_t acc_addr = tmem_base + ((q * 32u) << 16) + (buf * RB + rblk) * TILE_C;
@@ -1143,9 +1144,10 @@ uint32_t env_u32(const char *name, uint32_t dflt)
 //   RZ_TC_CONFIG 1..5 forces a block shape, RZ_TC_NOSPLIT=1 turns contraction splitting off, RZ_TC_EW_STAGES is the
 //   longest contraction (stages) that gets the sixteen-warp weight-gradient epilogue, RZ_TC_GROUP the rasterisation
 //   group (row tiles), RZ_TC_TMA_STORE=0 plain stores instead of bulk tensor stores, RZ_TC_VERBOSE=1 one line per launch,
-//   RZ_TC_UNIT_RANGES=0 keeps fully split launches on nsplit equal parts per block instead of equal stage ranges.
+//   RZ_TC_UNIT_RANGES=0 keeps fully split launches on nsplit equal parts per block instead of equal stage ranges,
+//   RZ_TC_DW_EW2=0 gives the two-row-block weight gradient eight epilogue warps instead of sixteen.
 struct Knobs {
-    std::atomic<uint32_t> config{0}, no_split{0}, ew_stages{64}, group{0}, tma_store{1}, verbose{0}, unit_ranges{1};
+    std::atomic<uint32_t> config{0}, no_split{0}, ew_stages{64}, group{0}, tma_store{1}, verbose{0}, unit_ranges{1}, dw_ew2{1};
     std::atomic<bool> ready{false};
 };
 Knobs g_knobs;
@@ -1159,6 +1161,7 @@ void load_knobs()
     g_knobs.tma_store.store(env_u32("RZ_TC_TMA_STORE", 1));
     g_knobs.verbose.store(env_u32("RZ_TC_VERBOSE", 0));
     g_knobs.unit_ranges.store(env_u32("RZ_TC_UNIT_RANGES", 1));
+    g_knobs.dw_ew2.store(env_u32("RZ_TC_DW_EW2", 1));
     g_knobs.ready.store(true, std::memory_order_release);
 }
 
@@ -1265,6 +1268,9 @@ TcConfig choose_config(const rz_problem *pb, int op)
         // one warp per scheduler) outlasts the main loop; sixteen epilogue warps hide its instruction latency.
         if (op == RZ_OP_BACKWARD_WEIGHT && !split && c.rb == 1 && stages / c.nsplit <= (int64_t)knobs().ew_stages.load(std::memory_order_relaxed))
             c.ew = 4;
+        // Two row blocks: the scatter cannot overlap the next block's MMAs, so it should at least be short - sixteen
+        // epilogue warps (two per TMEM lane quarter and row block) keep twice as many reductions in flight as eight.
+        if (op == RZ_OP_BACKWARD_WEIGHT && !split && c.rb == 2 && knobs().dw_ew2.load(std::memory_order_relaxed)) c.ew = 2;
         if (forced >= 1 && forced <= 5) {
             static const int order[5] = {2, 1, 0, 3, 4};
             if (order[forced - 1] == i) return c;
@@ -1502,6 +1508,10 @@ int launch_tc_any(const RzLaunchCtx &c, const CUtensorMap &mapA, const CUtensorM
         if (cfg.nc == 128)
             return tf32 ? launch_tc<OP, true, 1, 1, 0, 128, W>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 1, 1, 0, 128, W>(c, mapA, mapB, mapC, p, cfg);
         return tf32 ? launch_tc<OP, true, 1, 1, 0, 64, W>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 1, 1, 0, 64, W>(c, mapA, mapB, mapC, p, cfg);
+    }
+    if (OP == OP_DW && cfg.ctas == 2 && cfg.rb == 2 && cfg.ew == 2) {
+        constexpr int W = (OP == OP_DW) ? 2 : 1;
+        return tf32 ? launch_tc<OP, true, 2, 2, 0, 256, W>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 2, 2, 0, 256, W>(c, mapA, mapB, mapC, p, cfg);
     }
     if (cfg.ctas == 2 && cfg.rb == 2)
         return tf32 ? launch_tc<OP, true, 2, 2, 0, 256>(c, mapA, mapB, mapC, p, cfg) : launch_tc<OP, false, 2, 2, 0, 256>(c, mapA, mapB, mapC, p, cfg);
